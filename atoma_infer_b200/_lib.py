@@ -179,7 +179,14 @@ class HybridLayer(C.Structure):
                 [(n, C.c_float) for n in ("expert_limit", "shared_limit", "act_alpha", "act_up_shift")] +
                 [(n, C.c_void_p) for n in ("w_router", "w_shared_gate", "w_expert_gate_up", "w_expert_down", "w_ff_in")] +
                 [("side_part", C.c_int64)] +
-                [(n, C.c_void_p) for n in ("side_gate", "side_proj", "side_norm")])
+                [(n, C.c_void_p) for n in ("side_gate", "side_proj", "side_norm")] +
+                # blocks on residual lanes: softmax attention with a distance table, lane weights, biases, restricted routing
+                [("keep_first", C.c_int64), ("dist_rows", C.c_int64), ("dist_bias", C.c_void_p),
+                 ("values_are_keys", C.c_int32), ("out_gate", C.c_int32)] +
+                [(n, C.c_void_p) for n in ("lanes_in1", "lanes_out1", "lanes_mix1", "lanes_in2", "lanes_out2", "lanes_mix2",
+                                           "b_gate_up", "b_down", "router_correction")] +
+                [(n, C.c_int64) for n in ("route_groups", "route_keep", "identity_experts")] +
+                [("score_fn", C.c_int32), ("scale_input", C.c_int32)])
 
 
 class HybridModel(C.Structure):
@@ -190,7 +197,8 @@ class HybridModel(C.Structure):
                 [(n, C.c_void_p) for n in ("embed", "inv_freq", "final_norm", "head")] +
                 [("layers", C.POINTER(HybridLayer))] +
                 [("block_style", C.c_int32), ("norm_groups", C.c_int32), ("pos_table", C.c_void_p), ("max_positions", C.c_int64),
-                 ("logit_softcap", C.c_float), ("side_table", C.c_void_p), ("side_dim", C.c_int64), ("side_table_width", C.c_int64)])
+                 ("logit_softcap", C.c_float), ("side_table", C.c_void_p), ("side_dim", C.c_int64), ("side_table_width", C.c_int64),
+                 ("lanes", C.c_int32), ("embed_scale", C.c_float)])
 
 
 class GatedResidualArgs(C.Structure):
@@ -200,6 +208,26 @@ class GatedResidualArgs(C.Structure):
                 ("top", C.c_int64), ("gate", C.c_void_p), ("ld_gate", C.c_int64), ("gate_bias", C.c_void_p), ("x", C.c_void_p),
                 ("w_next", C.c_void_p), ("h", C.c_void_p), ("x_cast", C.c_void_p), ("T", C.c_int64), ("width", C.c_int64),
                 ("groups", C.c_int64), ("eps", C.c_float), ("weight_offset", C.c_float), ("dtype", C.c_uint32)]
+
+
+class LanesUpdateArgs(C.Structure):
+    """struct atoma_lanes_update_args"""
+
+    _fields_ = ([(n, C.c_void_p) for n in ("y", "y_bias", "expert_out", "pair_row", "top_expert", "top_weight", "h_in")] +
+                [("top", C.c_int64), ("experts", C.c_int64)] +
+                [(n, C.c_void_p) for n in ("x", "w_mix", "w_out", "w_in_next", "w_next", "h", "lane_sum")] +
+                [(n, C.c_int64) for n in ("T", "lanes", "width")] +
+                [("eps", C.c_float), ("weight_offset", C.c_float), ("dtype", C.c_uint32)])
+
+
+class SoftmaxAttnArgs(C.Structure):
+    """struct atoma_softmax_attn_args"""
+
+    _fields_ = ([(n, C.c_void_p) for n in ("q", "k_cache", "v_cache", "out", "gate")] + [("ld_gate", C.c_int64), ("dist_bias", C.c_void_p),
+                                                                                          ("dist_rows", C.c_int64)] +
+                [(n, C.c_void_p) for n in ("positions", "token_seq", "query_start", "block_tables")] +
+                [(n, C.c_int64) for n in ("T", "B", "max_blocks", "H", "G", "dim", "vdim", "block_size", "window", "keep_first")] +
+                [("scale", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32), ("max_seq_len", C.c_int32)])
 
 
 class LatentAttnArgs(C.Structure):
@@ -357,6 +385,15 @@ SIGNATURES = {
     "atoma_moe_workspace_bytes": (C.c_int64, [C.c_int64] * 5 + [C.c_uint32]),
     "atoma_moe_experts": (None, [C.POINTER(MoeArgs), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p]),
     "atoma_finish_logits_greedy": (None, [C.c_void_p] * 3 + [C.c_int64] * 2 + [C.c_float, C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_embed_scaled_lanes": (None, [C.c_void_p, C.c_void_p, C.c_float, C.c_void_p] + [C.c_int64] * 4 + [C.c_uint32, C.c_void_p]),
+    "atoma_lanes_read_norm": (None, [C.c_void_p] * 4 + [C.c_float, C.c_void_p, C.c_void_p] + [C.c_int64] * 3 + [C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_lanes_update_norm": (None, [C.POINTER(LanesUpdateArgs), C.c_void_p]),
+    "atoma_qk_headnorm_cache": (None, [C.c_void_p] + [C.c_int64] * 4 + [C.c_void_p, C.c_void_p, C.c_float] + [C.c_void_p] * 4 + [C.c_int64] * 5 +
+                                [C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_softmax_attention_paged": (None, [C.POINTER(SoftmaxAttnArgs), C.c_void_p]),
+    "atoma_moe_route_grouped": (None, [C.c_void_p] * 5 + [C.c_int64] * 6 + [C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]),
+    "atoma_glu_clamped_bias": (None, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_float, C.c_float,
+                                      C.c_uint32, C.c_void_p]),
     "atoma_hybrid_abi_sizeof": (C.c_int64, [C.c_int]),
     "atoma_hybrid_scratch_bytes": (C.c_int64, [C.POINTER(HybridModel), C.c_int64, C.c_int64]),
     "atoma_hybrid_step": (None, [C.POINTER(HybridModel), C.POINTER(HybridBatch), C.c_void_p]),

@@ -200,14 +200,16 @@ __global__ void __launch_bounds__(kRowThreads) unitnorm_add_norm_kernel(const T 
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) glu_clamped_kernel(const T *__restrict__ gu, int64_t ld, T *__restrict__ out, int64_t total, int ff,
-                                                          float limit, float alpha, float shift) {
+__global__ void __launch_bounds__(256) glu_clamped_kernel(const T *__restrict__ gu, int64_t ld, const float *__restrict__ bias,
+                                                          T *__restrict__ out, int64_t total, int ff, float limit, float alpha, float shift) {
     pdl_launch_dependents();
     pdl_wait();
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int64_t t = i / ff;
         const int j = static_cast<int>(i % ff);
-        out[i] = from_f<T>(glu_clamped(to_f(gu[t * ld + j]), to_f(gu[t * ld + ff + j]), limit, alpha, shift));
+        float g = to_f(gu[t * ld + j]), u = to_f(gu[t * ld + ff + j]);
+        if (bias) g += bias[j], u += bias[ff + j];
+        out[i] = from_f<T>(glu_clamped(g, u, limit, alpha, shift));
     }
 }
 
@@ -322,8 +324,8 @@ bool hyb_unitnorm_add_norm(const void *y, float *x, const float *w_unit, const f
 #undef CALL
 }
 
-bool hyb_glu_clamped(const void *gu, int64_t ld, void *out, int64_t T, int64_t ff, float limit, float alpha, float up_shift, uint32_t dtype,
-                     cudaStream_t stream) {
+bool hyb_glu_clamped_bias(const void *gu, int64_t ld, const float *bias, void *out, int64_t T, int64_t ff, float limit, float alpha,
+                          float up_shift, uint32_t dtype, cudaStream_t stream) {
     if (T <= 0 || ff <= 0) return true;
     if (!hybrid::known_dtype(dtype, "atoma_glu_clamped")) return false;
     if (!gu || !out || ld < 2 * ff) {
@@ -331,10 +333,15 @@ bool hyb_glu_clamped(const void *gu, int64_t ld, void *out, int64_t T, int64_t f
         return false;
     }
     const int64_t total = T * ff;
-#define CALL(TT) launch_ex(glu_clamped_kernel<TT>, dim3(flat_grid(total)), dim3(256), 0, stream, static_cast<const TT *>(gu), ld, \
+#define CALL(TT) launch_ex(glu_clamped_kernel<TT>, dim3(flat_grid(total)), dim3(256), 0, stream, static_cast<const TT *>(gu), ld, bias, \
                            static_cast<TT *>(out), total, static_cast<int>(ff), limit, alpha, up_shift)
     return hybrid::launched(HYB_DISPATCH(dtype, CALL), "glu_clamped_kernel");
 #undef CALL
+}
+
+bool hyb_glu_clamped(const void *gu, int64_t ld, void *out, int64_t T, int64_t ff, float limit, float alpha, float up_shift, uint32_t dtype,
+                     cudaStream_t stream) {
+    return hyb_glu_clamped_bias(gu, ld, nullptr, out, T, ff, limit, alpha, up_shift, dtype, stream);
 }
 
 }  // namespace atoma
@@ -373,4 +380,9 @@ extern "C" void atoma_glu_clamped(const void *gu, int64_t ld, void *out, int64_t
                                   uint32_t dtype, atoma_stream_t stream) {
     clear_status();
     hyb_glu_clamped(gu, ld, out, T, ff, limit, alpha, up_shift, dtype, static_cast<cudaStream_t>(stream));
+}
+extern "C" void atoma_glu_clamped_bias(const void *gu, int64_t ld, const float *bias, void *out, int64_t T, int64_t ff, float limit,
+                                       float alpha, float up_shift, uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    hyb_glu_clamped_bias(gu, ld, bias, out, T, ff, limit, alpha, up_shift, dtype, static_cast<cudaStream_t>(stream));
 }

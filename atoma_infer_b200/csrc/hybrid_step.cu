@@ -49,6 +49,16 @@ bool hyb_latent_expanded_ok(int64_t, int64_t, int64_t, uint32_t);
 bool hyb_latent_attention_expanded(const atoma_latent_expanded_args &, cudaStream_t);
 bool hyb_moe_route(const void *, const float *, const float *, int32_t *, float *, float *, int64_t, int64_t, int64_t, int64_t, int32_t,
                    uint32_t, cudaStream_t);
+bool hyb_moe_route_grouped(const void *, const float *, const float *, int32_t *, float *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
+                           int32_t, int32_t, uint32_t, cudaStream_t);
+bool hyb_embed_scaled_lanes(const uint32_t *, const void *, float, float *, int64_t, int64_t, int64_t, int64_t, uint32_t, cudaStream_t);
+bool hyb_lanes_read_norm(const float *, const float *, const int32_t *, const float *, float, void *, float *, int64_t, int64_t, int64_t, float,
+                         uint32_t, cudaStream_t);
+bool hyb_lanes_update_norm(const atoma_lanes_update_args &, cudaStream_t);
+bool hyb_qk_headnorm_cache(const void *, int64_t, int64_t, int64_t, int64_t, const float *, const float *, float, const int64_t *, void *, void *,
+                           void *, int64_t, int64_t, int64_t, int64_t, int64_t, float, uint32_t, cudaStream_t);
+bool hyb_softmax_attention(const atoma_softmax_attn_args &, cudaStream_t);
+bool hyb_glu_clamped_bias(const void *, int64_t, const float *, void *, int64_t, int64_t, float, float, float, uint32_t, cudaStream_t);
 int64_t hyb_moe_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t, uint32_t);
 bool hyb_moe_experts(const atoma_moe_args &, const void **, const int32_t **, cudaStream_t);
 
@@ -63,6 +73,11 @@ struct Widths {
 };
 
 inline bool gated(const float *bias) { return bias != nullptr; }
+
+// columns of the stacked projection of a softmax-attention layer: queries, keys, values (unless they are the keys), output gate
+inline int64_t softmax_proj_cols(const atoma_hybrid_layer &l) {
+    return l.heads * l.dim + l.kv_heads * l.dim + (l.values_are_keys ? 0 : l.kv_heads * l.vdim) + (l.out_gate ? l.heads * l.vdim : 0);
+}
 
 Widths widths(const atoma_hybrid_model &m, int64_t T) {
     Widths w;
@@ -83,6 +98,20 @@ Widths widths(const atoma_hybrid_model &m, int64_t T) {
                 }
             }
             if (l.side_gate) w.side = std::max(w.side, m.side_dim);
+            continue;
+        }
+        if (l.mixer == ATOMA_MIXER_SOFTMAX_ATTENTION) {
+            w.proj = std::max(w.proj, softmax_proj_cols(l));
+            w.q = std::max(w.q, l.heads * l.dim);
+            w.act = std::max(w.act, l.heads * l.vdim);
+            if (l.has_mlp) {
+                w.act = std::max(w.act, l.ff);
+                w.proj = std::max(w.proj, 2 * l.ff);
+                if (l.ff_kind == ATOMA_FF_MOE) {
+                    w.route = std::max(w.route, l.top);
+                    w.moe = std::max(w.moe, hyb_moe_workspace_bytes(T, l.top, l.experts, m.width, l.expert_ff, m.dtype));
+                }
+            }
             continue;
         }
         if (l.mixer == ATOMA_MIXER_SIGMOID_ATTENTION) {
@@ -123,7 +152,7 @@ Scratch carve(const atoma_hybrid_model &m, int64_t T, int64_t S, void *base) {
         off += up256(bytes);
         return p;
     };
-    s.x = reinterpret_cast<float *>(take(T * m.width * 4));
+    s.x = reinterpret_cast<float *>(take(T * std::max<int64_t>(1, m.lanes) * m.width * 4));
     s.h = take(T * m.width * es);
     s.proj = take(T * w.proj * es);
     s.q = take(T * w.q * es);
@@ -316,6 +345,136 @@ bool prenorm_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, con
     return true;
 }
 
+// One layer of a design on residual lanes: the mixer reads sum_s in1[s] x_s and writes back through mix1 / out1, the
+// feed-forward likewise with in2 / mix2 / out2.  s.h holds the mixer's normed input on entry and the next layer's (next_in /
+// next_norm, may be NULL) on return; lane_sum (may be NULL) receives the sum of the lanes after the layer.
+bool lanes_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, const atoma_hybrid_layer &l, const Scratch &s,
+                 const float *next_in, const float *next_norm, float *lane_sum, cudaStream_t stream) {
+    const uint32_t dt = m.dtype;
+    const int64_t es = dt == ATOMA_DTYPE_F32 ? 4 : 2;
+    const int64_t T = b.num_tokens, W = m.width;
+    if (l.mixer != ATOMA_MIXER_SOFTMAX_ATTENTION) {
+        set_status(kErrUnsupported, "atoma_hybrid_step: layers on residual lanes take the softmax-attention mixer, got %d", l.mixer);
+        return false;
+    }
+    if (!l.lanes_in1 || !l.lanes_out1 || !l.lanes_mix1 || (l.has_mlp && (!l.lanes_in2 || !l.lanes_out2 || !l.lanes_mix2))) {
+        set_status(kErrInvalidArg, "atoma_hybrid_step: a layer on residual lanes has no lane weights");
+        return false;
+    }
+    // ---- mixer: one product makes the queries, the keys (whose raw form is the values), and the output gate ----
+    const int64_t n_in = softmax_proj_cols(l);
+    const int64_t k_off = l.heads * l.dim;
+    const int64_t v_off = l.values_are_keys ? k_off : k_off + l.kv_heads * l.dim;
+    const int64_t g_off = v_off + (l.values_are_keys ? l.kv_heads * l.dim : l.kv_heads * l.vdim);
+    if (l.values_are_keys && l.vdim != l.dim) {
+        set_status(kErrInvalidArg, "atoma_hybrid_step: values that are the key projections need vdim = dim");
+        return false;
+    }
+    if (!hyb_linear(s.h, l.w_qkv, s.proj, T, n_in, W, dt, stream)) return false;
+    if (!hyb_qk_headnorm_cache(s.proj, n_in, 0, k_off, v_off, l.q_norm, l.k_norm, m.norm_offset, b.slot_mapping, s.q, l.k_cache, l.v_cache, T,
+                               l.heads, l.kv_heads, l.dim, l.vdim, m.eps, dt, stream))
+        return false;
+    atoma_softmax_attn_args a{};
+    a.q = s.q;
+    a.k_cache = l.k_cache;
+    a.v_cache = l.v_cache;
+    a.out = s.act;
+    a.gate = l.out_gate ? s.proj + g_off * es : nullptr;
+    a.ld_gate = n_in;
+    a.dist_bias = l.dist_bias;
+    a.dist_rows = l.dist_rows;
+    a.positions = b.positions;
+    a.token_seq = b.token_seq;
+    a.query_start = b.query_start;
+    a.block_tables = b.block_tables;
+    a.T = T;
+    a.B = b.num_seqs;
+    a.max_blocks = b.max_blocks;
+    a.H = l.heads;
+    a.G = l.kv_heads;
+    a.dim = l.dim;
+    a.vdim = l.vdim;
+    a.block_size = m.block_size;
+    a.window = l.window;
+    a.keep_first = l.keep_first;
+    a.scale = l.scale;
+    a.dtype = dt;
+    a.max_query_len = b.max_query_len;
+    a.max_seq_len = b.max_seq_len;
+    if (!hyb_softmax_attention(a, stream)) return false;
+    if (!hyb_linear(s.act, l.w_o, s.y, T, W, l.heads * l.vdim, dt, stream)) return false;
+    atoma_lanes_update_args u{};
+    u.y = s.y;
+    u.x = s.x;
+    u.w_mix = l.lanes_mix1;
+    u.w_out = l.lanes_out1;
+    u.w_in_next = l.has_mlp ? l.lanes_in2 : next_in;
+    u.w_next = l.has_mlp ? l.norm2 : next_norm;
+    u.h = s.h;
+    u.lane_sum = l.has_mlp ? nullptr : lane_sum;
+    u.T = T;
+    u.lanes = m.lanes;
+    u.width = W;
+    u.eps = m.eps;
+    u.weight_offset = m.norm_offset;
+    u.dtype = dt;
+    if (!hyb_lanes_update_norm(u, stream)) return false;
+    if (!l.has_mlp) return true;
+    // ---- feed-forward ----
+    atoma_lanes_update_args f = u;
+    f.y = nullptr;
+    f.w_mix = l.lanes_mix2;
+    f.w_out = l.lanes_out2;
+    f.w_in_next = next_in;
+    f.w_next = next_norm;
+    f.lane_sum = lane_sum;
+    if (l.ff > 0) {   // the dense feed-forward, or the shared expert of a mixture
+        const bool moe = l.ff_kind == ATOMA_FF_MOE;
+        if (!hyb_linear(s.h, moe ? l.w_ff_in : l.w_gate_up, s.proj, T, 2 * l.ff, W, dt, stream)) return false;
+        if (!hyb_glu_clamped_bias(s.proj, 2 * l.ff, moe ? nullptr : l.b_gate_up, s.act, T, l.ff, moe ? l.shared_limit : l.expert_limit,
+                                  l.act_alpha, l.act_up_shift, dt, stream))
+            return false;
+        if (!hyb_linear(s.act, l.w_down, s.y, T, W, l.ff, dt, stream)) return false;
+        f.y = s.y;
+        f.y_bias = moe ? nullptr : l.b_down;
+    }
+    if (l.ff_kind == ATOMA_FF_MOE) {
+        const int64_t outputs = l.experts + l.identity_experts;
+        if (!hyb_moe_route_grouped(s.h, l.w_router, l.router_correction, s.top_expert, s.top_weight, T, W, outputs, l.top, l.route_groups,
+                                   l.route_keep, l.score_fn, l.renormalize, dt, stream))
+            return false;
+        atoma_moe_args e{};
+        e.h = s.h;
+        e.top_expert = s.top_expert;
+        e.top_weight = s.top_weight;
+        e.w_gate_up = l.w_expert_gate_up;
+        e.w_down = l.w_expert_down;
+        e.workspace = s.moe;
+        e.workspace_bytes = s.moe_bytes;
+        e.T = T;
+        e.width = W;
+        e.experts = l.experts;
+        e.top = l.top;
+        e.ff = l.expert_ff;
+        e.limit = l.expert_limit;
+        e.alpha = l.act_alpha;   // alpha 1, shift 0, no limit: silu(gate) * up
+        e.up_shift = l.act_up_shift;
+        e.scale_input = l.scale_input;
+        e.dtype = dt;
+        const void *eo = nullptr;
+        const int32_t *pr = nullptr;
+        if (!hyb_moe_experts(e, &eo, &pr, stream)) return false;
+        f.expert_out = eo;
+        f.pair_row = pr;
+        f.top_expert = s.top_expert;
+        f.top_weight = s.top_weight;
+        f.h_in = s.h;
+        f.top = l.top;
+        f.experts = l.experts;
+    }
+    return hyb_lanes_update_norm(f, stream);
+}
+
 }  // namespace
 }  // namespace atoma
 
@@ -331,6 +490,8 @@ extern "C" int64_t atoma_hybrid_abi_sizeof(int which) {
         case 5: return sizeof(atoma_latent_attn_args);
         case 6: return sizeof(atoma_moe_args);
         case 7: return sizeof(atoma_latent_expanded_args);
+        case 8: return sizeof(atoma_lanes_update_args);
+        case 9: return sizeof(atoma_softmax_attn_args);
         default: return -1;
     }
 }
@@ -352,7 +513,7 @@ extern "C" void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_h
     const int64_t T = b.num_tokens, B = b.num_seqs, S = b.num_selected;
     if (T <= 0 || B <= 0) return;
     if (!b.tokens || !b.positions || !b.slot_mapping || !b.token_seq || !b.query_start || !b.context_lens || !b.block_tables ||
-        !b.state_slots || !b.scratch || (S > 0 && (!b.selected || !b.logits)) || !m.embed || (!m.inv_freq && !m.pos_table) || !m.final_norm ||
+        !b.state_slots || !b.scratch || (S > 0 && (!b.selected || !b.logits)) || !m.embed || (!m.inv_freq && !m.pos_table && m.block_style != ATOMA_BLOCK_LANES) || !m.final_norm ||
         !m.head || m.width <= 0 || m.vocab <= 0 || m.num_layers <= 0) {
         set_status(kErrInvalidArg, "atoma_hybrid_step: a required tensor is NULL");
         return;
@@ -371,6 +532,28 @@ extern "C" void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_h
     const int64_t W = m.width;
     const float off = m.norm_offset;
     const int64_t groups = m.norm_groups > 0 ? m.norm_groups : 1;
+    if (m.block_style == ATOMA_BLOCK_LANES) {
+        // scaled embedding into every lane; per layer the lanes are read, normed, run through the sublayer and written back
+        const int64_t lanes = m.lanes;
+        if (lanes < 1) {
+            set_status(kErrInvalidArg, "atoma_hybrid_step: a design on residual lanes needs at least one lane");
+            return;
+        }
+        if (!hyb_embed_scaled_lanes(b.tokens, m.embed, m.embed_scale, s.x, T, lanes, W, m.vocab, dt, stream)) return;
+        if (!hyb_lanes_read_norm(s.x, m.layers[0].lanes_in1, nullptr, m.layers[0].norm1, off, s.h, nullptr, T, lanes, W, m.eps, dt, stream)) return;
+        for (int64_t i = 0; i < m.num_layers; ++i) {
+            const bool last = i + 1 == m.num_layers;
+            if (!lanes_layer(m, b, m.layers[i], s, last ? nullptr : m.layers[i + 1].lanes_in1, last ? nullptr : m.layers[i + 1].norm1,
+                             b.residual_trace ? b.residual_trace + i * T * W : nullptr, stream))
+                return;
+        }
+        if (S > 0) {
+            if (!hyb_lanes_read_norm(s.x, nullptr, b.selected, m.final_norm, off, s.hs, nullptr, S, lanes, W, m.eps, dt, stream)) return;
+            if (!hyb_linear(s.hs, m.head, s.lg, S, m.vocab, W, dt, stream)) return;
+            if (!hyb_scale_greedy(s.lg, b.logits, b.next_tokens, S, m.vocab, m.logit_scale, m.logit_softcap, dt, stream)) return;
+        }
+        return;
+    }
     if (m.pos_table) {
         if (!hyb_embed_learned(b.tokens, b.positions, m.embed, m.pos_table, s.x, T, W, m.vocab, m.max_positions, dt, stream)) return;
     } else if (!hyb_embed_sinusoid(b.tokens, b.positions, m.embed, m.inv_freq, s.x, T, W, m.vocab, dt, stream)) {

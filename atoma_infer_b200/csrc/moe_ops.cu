@@ -167,6 +167,100 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float *__restrict__
         for (int k = 0; k < top; ++k) top_weight[t * top + k] /= total;
 }
 
+// Router with a restricted choice: one warp per token over the float32 logits of all router outputs.
+// s = softmax or sigmoid of the logits; c = s + correction; the outputs form `groups` equal groups of neighbours, a group's
+// score is its largest c, only the `keep` best groups (ties: the lower group) can be chosen from; `top` rounds of arg-max of c
+// among them (ties: the lower index); the weights are the chosen s, over their sum when renormalize.
+constexpr int kMaxRouteGroups = 64;
+__global__ void __launch_bounds__(32) moe_route_grouped_kernel(const float *__restrict__ z, const float *__restrict__ correction,
+                                                              int32_t *__restrict__ top_expert, float *__restrict__ top_weight, int outputs,
+                                                              int top, int groups, int keep, int score_fn, int renormalize) {
+    __shared__ float s_s[kMaxExperts], c_s[kMaxExperts], gbest[kMaxRouteGroups];
+    __shared__ int gkept[kMaxRouteGroups];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x;
+    const int64_t t = blockIdx.x;
+    const float *zr = z + t * outputs;
+    if (score_fn == ATOMA_SCORE_SOFTMAX) {
+        float m = -INFINITY;
+        for (int e = lane; e < outputs; e += 32) m = fmaxf(m, zr[e]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float sum = 0.f;
+        for (int e = lane; e < outputs; e += 32) {
+            const float v = expf(zr[e] - m);
+            s_s[e] = v;
+            sum += v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < outputs; e += 32) s_s[e] *= inv;
+    } else {
+        for (int e = lane; e < outputs; e += 32) s_s[e] = sigmoidf_(zr[e]);
+    }
+    for (int e = lane; e < outputs; e += 32) c_s[e] = s_s[e] + (correction ? correction[e] : 0.f);
+    __syncwarp();
+    if (groups > 1) {
+        const int per = outputs / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float b = -INFINITY;
+            for (int e = 0; e < per; ++e) b = fmaxf(b, c_s[g * per + e]);
+            gbest[g] = b;
+            gkept[g] = 0;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            for (int r = 0; r < keep; ++r) {
+                int bi = -1;
+                for (int g = 0; g < groups; ++g)
+                    if (!gkept[g] && (bi < 0 || gbest[g] > gbest[bi])) bi = g;
+                if (bi >= 0) gkept[bi] = 1;
+            }
+        }
+        __syncwarp();
+        for (int e = lane; e < outputs; e += 32)
+            if (!gkept[e / per]) c_s[e] = -INFINITY;
+        __syncwarp();
+    }
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int idx = 0x7fffffff;
+        for (int e = lane; e < outputs; e += 32) {
+            const float v = c_s[e];
+            if (v > best) {   // ascending e: the lower index wins a tie; chosen and excluded outputs are -inf
+                best = v;
+                idx = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ob > best || (ob == best && oi < idx)) {
+                best = ob;
+                idx = oi;
+            }
+        }
+        const bool found = idx != 0x7fffffff;
+        const float sv = found ? s_s[idx] : 0.f;
+        total += sv;
+        __syncwarp();
+        if (lane == 0) {
+            if (found) c_s[idx] = -INFINITY;
+            top_expert[t * top + k] = found ? idx : -1;
+            top_weight[t * top + k] = sv;
+        }
+        __syncwarp();
+    }
+    if (renormalize && lane == 0) {
+        const float inv = 1.0f / (total + 1e-20f);
+        for (int k = 0; k < top; ++k) top_weight[t * top + k] *= inv;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // pairs -> expert segments (one CTA)
 // meta[0] = row tiles in use, meta[1] = rows in use (padded), meta[2] = error word of the grouped products (reset here)
@@ -371,6 +465,44 @@ bool hyb_moe_route(const void *h, const float *w_router, const float *w_row_gate
                             "moe_topk_kernel");
 }
 
+bool hyb_moe_route_grouped(const void *h, const float *w_router, const float *correction, int32_t *top_expert, float *top_weight, int64_t T,
+                           int64_t width, int64_t outputs, int64_t top, int64_t groups, int64_t keep, int32_t score_fn, int32_t renormalize,
+                           uint32_t dtype, cudaStream_t stream) {
+    if (T <= 0) return true;
+    if (!hybrid::known_dtype(dtype, "atoma_moe_route_grouped")) return false;
+    if (groups <= 1) groups = 1, keep = 1;
+    if (!h || !w_router || !top_expert || !top_weight || width <= 0 || outputs <= 0 || outputs > kMaxExperts || top <= 0 || top > outputs ||
+        groups > kMaxRouteGroups || outputs % groups || keep <= 0 || keep > groups || (score_fn != ATOMA_SCORE_SIGMOID && score_fn != ATOMA_SCORE_SOFTMAX)) {
+        set_status(kErrInvalidArg, "atoma_moe_route_grouped: null argument, top %lld of %lld outputs (at most %d), or %lld of %lld groups (at most %d, equal sizes)",
+                   static_cast<long long>(top), static_cast<long long>(outputs), kMaxExperts, static_cast<long long>(keep),
+                   static_cast<long long>(groups), kMaxRouteGroups);
+        return false;
+    }
+    const int rows = static_cast<int>(outputs);
+    float *z = static_cast<float *>(get_workspace(stream, static_cast<size_t>(T) * rows * 4, kWorkspaceMoeRoute));
+    if (!z) return false;
+    const float *none = nullptr;
+    cudaError_t e;
+    if (T >= 256) {
+        const int64_t warps = ((T + 7) / 8) * ((rows + 3) / 4);
+#define CALL(TT) launch_ex(moe_logits_kernel<TT, 8, 4>, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 0, stream, \
+                           static_cast<const TT *>(h), w_router, none, z, static_cast<int>(T), static_cast<int>(width), rows, rows)
+        e = HYB_DISPATCH(dtype, CALL);
+#undef CALL
+    } else {
+        const int64_t warps = T * rows;
+#define CALL(TT) launch_ex(moe_logits_kernel<TT, 1, 1>, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 0, stream, \
+                           static_cast<const TT *>(h), w_router, none, z, static_cast<int>(T), static_cast<int>(width), rows, rows)
+        e = HYB_DISPATCH(dtype, CALL);
+#undef CALL
+    }
+    if (!hybrid::launched(e, "moe_logits_kernel")) return false;
+    return hybrid::launched(launch_ex(moe_route_grouped_kernel, dim3(static_cast<unsigned>(T)), dim3(32), 0, stream, static_cast<const float *>(z),
+                                      correction, top_expert, top_weight, rows, static_cast<int>(top), static_cast<int>(groups),
+                                      static_cast<int>(keep), static_cast<int>(score_fn), static_cast<int>(renormalize)),
+                            "moe_route_grouped_kernel");
+}
+
 int64_t hyb_moe_workspace_bytes(int64_t T, int64_t top, int64_t experts, int64_t width, int64_t ff, uint32_t dtype) {
     if (T < 0 || top <= 0 || experts <= 0 || width <= 0 || ff <= 0) return -1;
     const int64_t t = std::max<int64_t>(T, 1);   // either tile size may be chosen at run time
@@ -483,4 +615,11 @@ extern "C" void atoma_moe_experts(const atoma_moe_args *args, const void **exper
         return;
     }
     hyb_moe_experts(*args, expert_out, pair_row, static_cast<cudaStream_t>(stream));
+}
+extern "C" void atoma_moe_route_grouped(const void *h, const float *w_router, const float *correction, int32_t *top_expert, float *top_weight,
+                                        int64_t T, int64_t width, int64_t outputs, int64_t top, int64_t groups, int64_t keep, int32_t score_fn,
+                                        int32_t renormalize, uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    hyb_moe_route_grouped(h, w_router, correction, top_expert, top_weight, T, width, outputs, top, groups, keep, score_fn, renormalize, dtype,
+                          static_cast<cudaStream_t>(stream));
 }

@@ -1,8 +1,8 @@
 """Hybrid (attention + recurrent) decoder models: description, device layout and the step executor's host side.
 
-A model family (atoma_infer_b200/lilovik.py is the first, patadra.py the second) describes itself as a
-`HybridSpec` — a list of layer RUNS, each a mixer (sigmoid attention, minGRU or latent attention) with its
-sizes and constants and an optional feed-forward (gated dense, or a mixture of experts) — and hands over its
+A model family (atoma_infer_b200/lilovik.py is the first, patadra.py the second, nemasun.py the third) describes
+itself as a `HybridSpec` — a list of layer RUNS, each a mixer (sigmoid attention, minGRU, latent attention or softmax
+attention) with its sizes and constants and an optional feed-forward (gated dense, or a mixture of experts) — and hands over its
 weights under the generic names below.  A design that runs a span of layers several times lists every run;
 runs that name the same `source` share one copy of the weights and have caches of their own.  `HybridExecutor` lays them out
 on the device, owns the paged key/value caches and the recurrent-state slots, and runs one step of a MIXED
@@ -21,6 +21,13 @@ Pre-norm designs (block_style "prenorm"):
   w_uq [H dim, q_rank]   w_uk [H dim, kv_rank]   w_uv [H vdim, kv_rank]   dq_norm, dkv_norm, sink, gate biases: float32
   w_ff_in [2 shared_ff (+ width), width]   w_down [width, shared_ff]   w_router [experts, width] float32
   w_expert_gate_up [experts, 2 ff, width]   w_expert_down [experts, width, ff]   side_gate, side_proj, side_norm
+Designs on residual lanes (block_style "lanes"):
+  w_qkv [H dim + G dim (+ G vdim unless the values are the keys) (+ H vdim with an output gate), width]   w_o [width, H vdim]
+  q_norm, k_norm [dim]   dist_bias [rows, H] float32 (bias by query-key distance, the last row for every larger distance)
+  lanes_in1/out1 [lanes], lanes_mix1 [lanes, lanes] (and ..2 for the feed-forward), all float32
+  dense: w_gate_up [2 ff, width], b_gate_up [2 ff], w_down [width, ff], b_down [width]
+  experts: w_router [experts + identity, width] float32, router_correction [same], w_expert_gate_up, w_expert_down,
+           shared expert w_ff_in [2 shared_ff, width], w_down [width, shared_ff]
 """
 from __future__ import annotations
 
@@ -38,9 +45,10 @@ from .ops import AtomaError
 from .scheduler import StepPlan
 from .worker import InputStager, SequenceInput
 
-MIXER_ATTENTION, MIXER_MINGRU, MIXER_LATENT = 0, 1, 2
+MIXER_ATTENTION, MIXER_MINGRU, MIXER_LATENT, MIXER_SOFTMAX = 0, 1, 2, 3
 LONG_PORTION = 128        # tokens of a sequence in one step from which latent attention runs on expanded keys and values
-BLOCK_STYLES = {"sandwich": 0, "prenorm": 1}
+BLOCK_STYLES = {"sandwich": 0, "prenorm": 1, "lanes": 2}
+SCORE_FNS = {"sigmoid": 0, "softmax": 1}
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
 DTYPE_CODES = {torch.bfloat16: 1, torch.float32: 2}
 
@@ -83,8 +91,36 @@ class LatentAttentionSpec:
 
 
 @dataclass(frozen=True)
+class SoftmaxAttentionSpec:
+    """Softmax attention with grouped key/value heads, a per-head q/k RMS norm, a window that also keeps the first tokens,
+    a bias looked up by query-key distance, and an optional sigmoid gate on the heads' outputs."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int = 0                # 0 = every earlier token is visible
+    keep_first: int = 0            # tokens at the start of the sequence that stay visible behind the window
+    values_are_keys: bool = False  # no value projection: the values are the key projections before their norm
+    out_gate: bool = False         # heads' outputs times sigmoid(W h) before the output projection
+    distance_bias: bool = False    # weights carry dist_bias [rows, heads]
+
+
+@dataclass(frozen=True)
+class ClampedMlpSpec:
+    """Dense feed-forward W_down (g sigmoid(alpha g) (u + up_shift)) on g = min(W_gate h + b, limit), u = clamp(W_up h + b)."""
+    ff: int
+    limit: float = 0.0
+    alpha: float = 1.702
+    up_shift: float = 1.0
+    bias: bool = True
+
+
+@dataclass(frozen=True)
 class MoeSpec:
-    """Sigmoid-routed experts with a clamped gated activation g sigmoid(alpha g) (u + up_shift), and an optional shared expert."""
+    """Routed experts with a clamped gated activation g sigmoid(alpha g) (u + up_shift), and an optional shared expert.
+    The defaults are a sigmoid router that scales the experts' inputs; `score`, `correction`, `groups` / `keep_groups`,
+    `identity` and `scale_input` describe routers whose choice is corrected and restricted and whose weights scale outputs."""
     experts: int
     top: int
     ff: int
@@ -95,16 +131,24 @@ class MoeSpec:
     alpha: float = 1.702
     up_shift: float = 1.0
     renormalize: bool = False      # chosen scores divided by their sum
+    score: str = "sigmoid"         # "sigmoid" | "softmax" over all router outputs
+    correction: bool = False       # a per-output term added to the scores for the choice only
+    groups: int = 1                # router outputs form this many equal groups of neighbours ...
+    keep_groups: int = 1           # ... of which only the best may be chosen from
+    identity: int = 0              # router outputs after the experts that hand the token's input through
+    scale_input: bool = True       # the router's weight multiplies the expert's input (False: its output)
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    mixer: str                               # "attention" | "mingru" | "latent_attention"
+    mixer: str                               # "attention" | "mingru" | "latent_attention" | "softmax_attention"
     attention: Optional[AttentionSpec] = None
     mingru: Optional[MinGruSpec] = None
     mlp: Optional[MlpSpec] = None
     latent: Optional[LatentAttentionSpec] = None
     moe: Optional[MoeSpec] = None
+    softmax: Optional[SoftmaxAttentionSpec] = None
+    clamped_mlp: Optional[ClampedMlpSpec] = None
     gated_residual: bool = False             # sublayer results times sigmoid(W h + b) before they join the stream
     side_part: Optional[int] = None          # which part of the token side table the layer reads; None = no side input
     source: Optional[int] = None             # entry of weights["layers"] the run uses; None = its own index
@@ -125,6 +169,8 @@ class HybridSpec:
     max_positions: int = 0
     logit_softcap: float = 0.0               # logits <- cap * tanh(logits / cap); 0 = none
     side_dim: int = 0                        # width of one layer's part of the token side table
+    lanes: int = 0                           # block_style "lanes": copies of the residual stream
+    embed_scale: float = 1.0                 # block_style "lanes": the embedding row times this (no position signal)
 
     @property
     def has_state(self) -> bool:
@@ -133,6 +179,7 @@ class HybridSpec:
     def cache_bytes_per_token(self, dtype: torch.dtype) -> int:
         es = torch.empty((), dtype=dtype).element_size()
         return (sum(l.attention.kv_heads * (l.attention.dim + l.attention.vdim) * es for l in self.layers if l.mixer == "attention") +
+                sum(l.softmax.kv_heads * (l.softmax.dim + l.softmax.vdim) * es for l in self.layers if l.mixer == "softmax_attention") +
                 sum(l.latent.kv_rank * es for l in self.layers if l.mixer == "latent_attention"))
 
 
@@ -173,7 +220,10 @@ class HybridExecutor:
         self.embed, self.head = big(weights["embed"]), big(weights["head"])
         self.final_norm = small(weights["final_norm"])
         self.inv_freq = self.pos_table = self.side_table = None
-        if spec.position == "learned":
+        if spec.block_style == "lanes":
+            if not 1 <= spec.lanes <= 16:
+                raise AtomaError(f"{spec.lanes} residual lanes (1 to 16 are supported)")
+        elif spec.position == "learned":
             self.pos_table = big(weights["pos"])
             if self.pos_table.shape[0] < spec.max_positions or spec.max_positions <= 0:
                 raise AtomaError(f"position table of {self.pos_table.shape[0]} rows for {spec.max_positions} positions")
@@ -194,6 +244,21 @@ class HybridExecutor:
             L = self._layers[i]
             src = i if ls.source is None else ls.source
             w = weights["layers"][src]
+            if spec.block_style == "lanes":
+                if src in placed:
+                    C.memmove(C.byref(L), C.byref(placed[src]), C.sizeof(HybridLayer))
+                else:
+                    self._place_lanes(L, i, ls, w, big, small)
+                    placed[src] = L
+                a = ls.softmax
+                kc = torch.zeros((rows, a.kv_heads, a.dim), dtype=dtype, device=dev)
+                vc = torch.zeros((rows, a.kv_heads, a.vdim), dtype=dtype, device=dev)
+                L.k_cache, L.v_cache = kc.data_ptr(), vc.data_ptr()
+                self.k_caches.append(kc)
+                self.v_caches.append(vc)
+                self.states.append(None)
+                self.latent_caches.append(None)
+                continue
             if spec.block_style == "prenorm":
                 if src in placed:
                     C.memmove(C.byref(L), C.byref(placed[src]), C.sizeof(HybridLayer))     # same weights, a cache of its own below
@@ -256,6 +321,7 @@ class HybridExecutor:
         m.max_positions, m.logit_softcap = spec.max_positions, spec.logit_softcap
         if self.side_table is not None:
             m.side_table, m.side_dim, m.side_table_width = self.side_table.data_ptr(), spec.side_dim, self.side_table.shape[1]
+        m.lanes, m.embed_scale = spec.lanes, spec.embed_scale
         self._model = m
         self._stager = InputStager(device=dev, block_size=self.block_size, enable_chunked_prefill=True)
         self._extra_host = None
@@ -304,6 +370,71 @@ class HybridExecutor:
             L.side_part = ls.side_part
             L.side_gate, L.side_proj = big(w["side_gate"]).data_ptr(), big(w["side_proj"]).data_ptr()
             L.side_norm = small(w["side_norm"]).data_ptr()
+
+    def _place_lanes(self, L, i: int, ls: LayerSpec, w: dict, big, small) -> None:
+        """Device copies and sizes of one layer on residual lanes (softmax attention; dense or routed feed-forward or none)."""
+        if ls.mixer != "softmax_attention" or ls.softmax is None:
+            raise AtomaError(f"layer {i}: blocks on residual lanes take the softmax-attention mixer, not {ls.mixer!r}")
+        a, S = ls.softmax, self.spec.lanes
+        if a.heads % a.kv_heads:
+            raise AtomaError(f"layer {i}: {a.kv_heads} kv heads do not divide {a.heads} heads")
+        if a.values_are_keys and a.vdim != a.dim:
+            raise AtomaError(f"layer {i}: values that are the key projections need vdim = dim, got {a.vdim} and {a.dim}")
+        L.mixer = MIXER_SOFTMAX
+        L.heads, L.kv_heads, L.dim, L.vdim = a.heads, a.kv_heads, a.dim, a.vdim
+        L.scale, L.window, L.keep_first = a.scale, a.window, a.keep_first
+        L.values_are_keys, L.out_gate = int(a.values_are_keys), int(a.out_gate)
+        n_in = a.heads * a.dim + a.kv_heads * a.dim + (0 if a.values_are_keys else a.kv_heads * a.vdim) + (a.heads * a.vdim if a.out_gate else 0)
+        if tuple(w["w_qkv"].shape) != (n_in, self.spec.width):
+            raise AtomaError(f"layer {i}: stacked projection of shape {tuple(w['w_qkv'].shape)}, expected {(n_in, self.spec.width)}")
+        L.norm1 = small(w["norm1"]).data_ptr()
+        L.w_qkv, L.w_o = big(w["w_qkv"]).data_ptr(), big(w["w_o"]).data_ptr()
+        L.q_norm, L.k_norm = small(w["q_norm"]).data_ptr(), small(w["k_norm"]).data_ptr()
+        if a.distance_bias:
+            db = small(w["dist_bias"])
+            if db.dim() != 2 or db.shape[1] != a.heads or db.shape[0] < 1:
+                raise AtomaError(f"layer {i}: distance table of shape {tuple(db.shape)} for {a.heads} heads")
+            L.dist_bias, L.dist_rows = db.data_ptr(), db.shape[0]
+
+        def lane_weights(q):
+            t_in, t_out, t_mix = small(w[f"lanes_in{q}"]), small(w[f"lanes_out{q}"]), small(w[f"lanes_mix{q}"])
+            if tuple(t_in.shape) != (S,) or tuple(t_out.shape) != (S,) or tuple(t_mix.shape) != (S, S):
+                raise AtomaError(f"layer {i}: lane weights of shapes {tuple(t_in.shape)}, {tuple(t_out.shape)}, {tuple(t_mix.shape)} for {S} lanes")
+            return t_in.data_ptr(), t_out.data_ptr(), t_mix.data_ptr()
+
+        L.lanes_in1, L.lanes_out1, L.lanes_mix1 = lane_weights(1)
+        if ls.clamped_mlp is None and ls.moe is None:
+            L.has_mlp = 0
+            return
+        L.has_mlp = 1
+        L.norm2 = small(w["norm2"]).data_ptr()
+        L.lanes_in2, L.lanes_out2, L.lanes_mix2 = lane_weights(2)
+        if ls.clamped_mlp is not None:
+            f = ls.clamped_mlp
+            L.ff_kind, L.ff = 0, f.ff
+            L.expert_limit, L.act_alpha, L.act_up_shift = f.limit, f.alpha, f.up_shift
+            L.w_gate_up, L.w_down = big(w["w_gate_up"]).data_ptr(), big(w["w_down"]).data_ptr()
+            if f.bias:
+                L.b_gate_up, L.b_down = small(w["b_gate_up"]).data_ptr(), small(w["b_down"]).data_ptr()
+            return
+        e = ls.moe
+        outputs = e.experts + e.identity
+        if e.score not in SCORE_FNS:
+            raise AtomaError(f"layer {i}: unknown router score {e.score!r}")
+        if not 0 < e.top <= outputs or e.experts < 1:
+            raise AtomaError(f"layer {i}: top {e.top} of {outputs} router outputs ({e.experts} experts)")
+        if e.groups < 1 or outputs % e.groups or not 1 <= e.keep_groups <= e.groups:
+            raise AtomaError(f"layer {i}: {outputs} router outputs in {e.groups} groups, {e.keep_groups} kept")
+        L.ff_kind, L.renormalize, L.score_fn, L.scale_input = 1, int(e.renormalize), SCORE_FNS[e.score], int(e.scale_input)
+        L.experts, L.top, L.expert_ff, L.ff = e.experts, e.top, e.ff, e.shared_ff
+        L.identity_experts, L.route_groups, L.route_keep = e.identity, e.groups, e.keep_groups
+        L.expert_limit, L.shared_limit, L.act_alpha, L.act_up_shift = e.limit, e.shared_limit, e.alpha, e.up_shift
+        L.w_router = small(w["w_router"]).data_ptr()
+        if e.correction:
+            L.router_correction = small(w["router_correction"]).data_ptr()
+        L.w_expert_gate_up, L.w_expert_down = big(w["w_expert_gate_up"]).data_ptr(), big(w["w_expert_down"]).data_ptr()
+        if e.shared_ff > 0:
+            L.w_ff_in, L.w_down = big(w["w_ff_in"]).data_ptr(), big(w["w_down"]).data_ptr()
 
     # ---- buffers (grow-only) ----
     def _reserve(self, T: int, S: int) -> None:

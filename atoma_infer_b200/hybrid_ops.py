@@ -300,3 +300,115 @@ def latent_attention_expanded(q, cache, w_uk, w_uv, query_start, context_lens, b
     _lib.lib().atoma_latent_attention_expanded(C.byref(a), _s())
     _check()
     return out
+
+
+# ---- residual lanes, softmax attention with a distance table, restricted routing ----
+def embed_scaled_lanes(tokens, table, scale, lanes):
+    T, W = tokens.numel(), table.shape[1]
+    x = torch.empty((T, lanes, W), dtype=torch.float32, device=table.device)
+    _lib.lib().atoma_embed_scaled_lanes(_p(tokens), _p(table), scale, _p(x), T, lanes, W, table.shape[0], _CODES[table.dtype], _s())
+    _check()
+    return x
+
+
+def lanes_read_norm(x, w_in, weight, offset, eps, dtype, rows=None, want_sum=False):
+    """x float32 [T, lanes, width] -> (normed read in `dtype`, the un-normed read as float32 or None)."""
+    T, S, W = x.shape
+    R = T if rows is None else rows.numel()
+    out = torch.empty((R, W), dtype=dtype, device=x.device)
+    u = torch.empty((R, W), dtype=torch.float32, device=x.device) if want_sum else None
+    _lib.lib().atoma_lanes_read_norm(_p(x), _p(w_in), _p(rows), _p(weight), offset, _p(out), _p(u), R, S, W, eps, _CODES[dtype], _s())
+    _check()
+    return out, u
+
+
+def lanes_update_norm(x, y, w_mix, w_out, dtype, eps=1e-5, offset=0.0, y_bias=None, w_in_next=None, w_next=None, expert_out=None,
+                      pair_row=None, top_expert=None, top_weight=None, h_in=None, experts=0, want_lane_sum=False):
+    """x is updated in place; returns (next normed read or None, lane sum or None)."""
+    from ._lib import LanesUpdateArgs
+    T, S, W = x.shape
+    h = torch.empty((T, W), dtype=dtype, device=x.device) if w_next is not None else None
+    ls = torch.empty((T, W), dtype=torch.float32, device=x.device) if want_lane_sum else None
+    a = LanesUpdateArgs()
+    a.y, a.y_bias, a.expert_out, a.pair_row = _p(y), _p(y_bias), expert_out if isinstance(expert_out, int) else _p(expert_out), \
+        pair_row if isinstance(pair_row, int) else _p(pair_row)
+    a.top_expert, a.top_weight, a.h_in = _p(top_expert), _p(top_weight), _p(h_in)
+    a.top, a.experts = (top_expert.shape[1] if top_expert is not None else 0), experts
+    a.x, a.w_mix, a.w_out, a.w_in_next, a.w_next, a.h, a.lane_sum = _p(x), _p(w_mix), _p(w_out), _p(w_in_next), _p(w_next), _p(h), _p(ls)
+    a.T, a.lanes, a.width, a.eps, a.weight_offset, a.dtype = T, S, W, eps, offset, _CODES[dtype]
+    _lib.lib().atoma_lanes_update_norm(C.byref(a), _s())
+    _check()
+    return h, ls
+
+
+def qk_headnorm_cache(proj, q_off, k_off, v_off, q_w, k_w, offset, slots, k_cache, v_cache, H, G, dim, vdim, eps):
+    T = proj.shape[0]
+    q = torch.empty((T, H * dim), dtype=proj.dtype, device=proj.device)
+    _lib.lib().atoma_qk_headnorm_cache(_p(proj), proj.stride(0), q_off, k_off, v_off, _p(q_w), _p(k_w), offset, _p(slots), _p(q), _p(k_cache),
+                                       _p(v_cache), T, H, G, dim, vdim, eps, _CODES[proj.dtype], _s())
+    _check()
+    return q
+
+
+def softmax_attention_paged(q, k_cache, v_cache, positions, token_seq, block_tables, H, G, dim, vdim, block_size, scale, window=0,
+                            keep_first=0, dist_bias=None, gate=None, max_query_len=None, query_start=None, max_seq_len=None):
+    from ._lib import SoftmaxAttnArgs
+    T = q.shape[0]
+    if query_start is None:
+        counts = torch.bincount(token_seq.long(), minlength=block_tables.shape[0])
+        query_start = torch.cat([counts.new_zeros(1), counts.cumsum(0)]).to(torch.int32)
+    if max_query_len is None:
+        max_query_len = int((query_start[1:] - query_start[:-1]).max())
+    if max_seq_len is None:
+        max_seq_len = int(positions.max()) + 1
+    out = torch.empty((T, H * vdim), dtype=q.dtype, device=q.device)
+    a = SoftmaxAttnArgs()
+    a.q, a.k_cache, a.v_cache, a.out, a.gate = _p(q), _p(k_cache), _p(v_cache), _p(out), _p(gate)
+    a.ld_gate = gate.stride(0) if gate is not None else 0
+    a.dist_bias, a.dist_rows = _p(dist_bias), (dist_bias.shape[0] if dist_bias is not None else 0)
+    a.positions, a.token_seq, a.query_start, a.block_tables = _p(positions), _p(token_seq), _p(query_start), _p(block_tables)
+    a.T, a.B, a.max_blocks, a.H, a.G, a.dim, a.vdim = T, block_tables.shape[0], block_tables.shape[1], H, G, dim, vdim
+    a.block_size, a.window, a.keep_first, a.scale, a.dtype = block_size, window, keep_first, scale, _CODES[q.dtype]
+    a.max_query_len, a.max_seq_len = int(max_query_len), int(max_seq_len)
+    _lib.lib().atoma_softmax_attention_paged(C.byref(a), _s())
+    _check()
+    return out
+
+
+def moe_route_grouped(h, w_router, correction, top, groups=1, keep=1, score="softmax", renormalize=True):
+    T, E = h.shape[0], w_router.shape[0]
+    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    wgt = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    _lib.lib().atoma_moe_route_grouped(_p(h), _p(w_router), _p(correction), _p(idx), _p(wgt), T, h.shape[1], E, top, groups, keep,
+                                       1 if score == "softmax" else 0, 1 if renormalize else 0, _CODES[h.dtype], _s())
+    _check()
+    return idx, wgt
+
+
+def glu_clamped_bias(gu, bias, ff, limit, alpha, up_shift):
+    T = gu.shape[0]
+    out = torch.empty((T, ff), dtype=gu.dtype, device=gu.device)
+    _lib.lib().atoma_glu_clamped_bias(_p(gu), gu.stride(0), _p(bias), _p(out), T, ff, limit, alpha, up_shift, _CODES[gu.dtype], _s())
+    _check()
+    return out
+
+
+def moe_expert_rows(h, top_expert, top_weight, w_gate_up, w_down, limit, alpha, up_shift, scale_input=False):
+    """The routed experts' result rows as the step executor sees them: (expert_out address, pair_row address, workspace tensor
+    that owns both).  For callers that hand them to lanes_update_norm."""
+    from ._lib import MoeArgs
+    T, W = h.shape
+    E, ff2, _ = w_gate_up.shape
+    top = top_expert.shape[1]
+    code = _CODES[h.dtype]
+    nbytes = int(_lib.lib().atoma_moe_workspace_bytes(T, top, E, W, ff2 // 2, code))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=h.device)
+    a = MoeArgs()
+    a.h, a.top_expert, a.top_weight, a.w_gate_up, a.w_down = _p(h), _p(top_expert), _p(top_weight), _p(w_gate_up), _p(w_down)
+    a.workspace, a.workspace_bytes = _p(ws), nbytes
+    a.T, a.width, a.experts, a.top, a.ff = T, W, E, top, ff2 // 2
+    a.limit, a.alpha, a.up_shift, a.scale_input, a.dtype = limit, alpha, up_shift, 1 if scale_input else 0, code
+    eo, pr = C.c_void_p(), C.c_void_p()
+    _lib.lib().atoma_moe_experts(C.byref(a), C.byref(eo), C.byref(pr), _s())
+    _check()
+    return eo.value, pr.value, ws

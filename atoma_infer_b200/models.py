@@ -71,6 +71,14 @@ def _build_patadra(cfg, ckpt, dtype, device, cache: CacheConfig):
     return HybridExecutor(spec, weights, dtype, device, cache.num_blocks, cache.block_size, cache.num_state_slots)
 
 
+def _build_nemasun(cfg, ckpt, dtype, device, cache: CacheConfig):
+    from . import nemasun
+    from .hybrid import HybridExecutor
+    spec = nemasun.spec_from_config(cfg)
+    weights = nemasun.weights_from_checkpoint(spec, cfg, ckpt)
+    return HybridExecutor(spec, weights, dtype, device, cache.num_blocks, cache.block_size, cache.num_state_slots)
+
+
 def _build_llama(cfg, ckpt, dtype, device, cache: CacheConfig):
     from .llama_engine import LlamaExecutor
     return LlamaExecutor.from_checkpoint(cfg, ckpt, dtype, device, cache)
@@ -78,4 +86,5 @@ def _build_llama(cfg, ckpt, dtype, device, cache: CacheConfig):
 
 register_model("Lilovik", _build_lilovik, _lilovik_needs_state)
 register_model("Patadra", _build_patadra)
+register_model("Nemasun", _build_nemasun)
 register_model("LlamaForCausalLM", _build_llama)

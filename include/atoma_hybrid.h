@@ -19,6 +19,16 @@
  * looked up in a side table, and a tanh cap on the logits.  A span of layers may run several times
  * with the same weights; every run is one entry of the layer list with a cache of its own.
  *
+ * The third design is Nemasun: a scaled embedding without a position signal, several residual LANES
+ * (copies of the residual stream; every sublayer reads a weighted sum of them and writes its result
+ * back through a lane-mixing matrix — the arrangement known as hyper-connections), softmax attention
+ * with grouped key/value heads whose values are the un-normed key projections, a per-head q/k RMS
+ * norm, a learned bias looked up by query-key distance, a sliding window that also keeps the first
+ * tokens of the sequence, and a sigmoid gate on the heads' outputs; a clamped gated feed-forward with
+ * biases; and a mixture of experts with a softmax router whose choice (not its weights) carries a
+ * per-output correction and is restricted to the best groups of neighbouring outputs, with identity
+ * experts (router outputs that hand the token's input through) and an ungated shared expert.
+ *
  * Conventions: row-major; `dtype` is the number format of activations, large weights and the caches:
  * 1 = bfloat16, 2 = float32 (true 32-bit arithmetic: no reduced-precision matrix mode).  Whatever the
  * dtype, the residual stream, norm statistics, attention scores and weights, recurrent state and all
@@ -269,10 +279,107 @@ void atoma_finish_logits_greedy(const void *logits, float *logits_f32, uint32_t 
                                 float softcap, uint32_t dtype, atoma_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------ */
+/* Residual lanes, softmax attention with a distance table, grouped routing                     */
+/* ------------------------------------------------------------------------------------------ */
+
+/* x[t, s, :] = table[tokens[t], :] * scale for every lane s < lanes; x float32 [T, lanes, width]. */
+void atoma_embed_scaled_lanes(const uint32_t *tokens, const void *table, float scale, float *x, int64_t T, int64_t lanes, int64_t width,
+                              int64_t vocab, uint32_t dtype, atoma_stream_t stream);
+
+/* A sublayer's input from the lanes: u = sum_s w_in[s] x[r, s, :] (w_in NULL: the plain sum), r = rows ? rows[i] : i;
+ * out[i, :] = u / sqrt(mean(u^2) + eps) * (weight_offset + weight) in `dtype`; sum_out (float32 [R, width], may be NULL) = u. */
+void atoma_lanes_read_norm(const float *x, const float *w_in, const int32_t *rows, const float *weight, float weight_offset, void *out,
+                           float *sum_out, int64_t R, int64_t lanes, int64_t width, float eps, uint32_t dtype, atoma_stream_t stream);
+
+/*
+ * A sublayer's result written back to the lanes, fused with the NEXT sublayer's read and norm.  Per token t, channel c:
+ *   v = (y ? y[t, c] : 0) + (y_bias ? y_bias[c] : 0)
+ *       + sum_{k < top} (top_expert[t, k] in [0, experts):  expert_out[pair_row[t top + k], c]
+ *                        top_expert[t, k] >= experts:        top_weight[t, k] * h_in[t, c]       (identity expert)
+ *                        top_expert[t, k] < 0:               nothing)
+ *   x'[t, s2, c] = sum_s w_mix[s, s2] x[t, s, c] + w_out[s2] v           (all lanes from the old ones)
+ *   u = sum_s w_in_next[s] x'[t, s, c];  h[t, :] = u / sqrt(mean(u^2) + eps) * (weight_offset + w_next)    (w_next NULL: no read)
+ *   lane_sum[t, c] = sum_s x'[t, s, c]                                                                    (NULL: not written)
+ * y, expert_out, h_in, h in `dtype`; x float32 [T, lanes, width] in place.  h_in and h may be the same buffer.
+ * The experts' rows are added in the order k = 0 .. top - 1.
+ */
+typedef struct atoma_lanes_update_args {
+    const void *y;                /* [T, width] or NULL */
+    const float *y_bias;          /* [width] or NULL */
+    const void *expert_out;       /* rows of the routed experts' results, or NULL */
+    const int32_t *pair_row;      /* [T top] */
+    const int32_t *top_expert;    /* [T top] */
+    const float *top_weight;      /* [T top] */
+    const void *h_in;             /* [T, width]: what identity experts hand through */
+    int64_t top, experts;
+    float *x;                     /* [T, lanes, width] */
+    const float *w_mix, *w_out;   /* [lanes, lanes] indexed [from, to]; [lanes] */
+    const float *w_in_next;       /* [lanes] or NULL (plain sum) */
+    const float *w_next;          /* [width] or NULL */
+    void *h;                      /* [T, width] */
+    float *lane_sum;              /* [T, width] or NULL */
+    int64_t T, lanes, width;
+    float eps, weight_offset;
+    uint32_t dtype;
+} atoma_lanes_update_args;
+void atoma_lanes_update_norm(const atoma_lanes_update_args *args, atoma_stream_t stream);
+
+/* After a fused projection proj[t, :] (row stride ld) that holds the queries at column q_off (H heads of dim), the keys at
+ * k_off (G heads of dim) and the values at v_off (G heads of vdim; v_off = k_off: the values ARE the key projections):
+ *   q_out[t, h, :] = proj_q / sqrt(mean over the head's dim + eps) * (weight_offset + q_weight)     (one weight [dim] for all heads)
+ *   k_cache[slot_mapping[t], g, :] = the same with k_weight;   v_cache[slot, g, :] = the values as projected (no norm)
+ * caches [num_blocks * block_size, G, dim] / [.., G, vdim] in `dtype`; slot < 0 is skipped. */
+void atoma_qk_headnorm_cache(const void *proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off, const float *q_weight,
+                             const float *k_weight, float weight_offset, const int64_t *slot_mapping, void *q_out, void *k_cache,
+                             void *v_cache, int64_t T, int64_t H, int64_t G, int64_t dim, int64_t vdim, float eps, uint32_t dtype,
+                             atoma_stream_t stream);
+
+/*
+ * Softmax attention over a paged cache for a mixed batch, grouped key/value heads (head h reads kv head h / (H / G)).
+ * Query token t of sequence b at position p sees key j <= p if p - j < window (window <= 0: no limit) or j < keep_first.
+ *   s_h(j) = (q_h . k_j) * scale + (dist_bias ? dist_bias[min(p - j, dist_rows - 1), h] : 0)
+ *   out[t, h, :] = softmax_j(s_h) v_j * (gate ? sigmoid(gate[t, h vdim ..]) : 1)
+ * Scores, weights, maxima and sums are float32.  gate (row stride ld_gate) and out in `dtype`.
+ */
+typedef struct atoma_softmax_attn_args {
+    const void *q;                /* [T, H dim] */
+    const void *k_cache, *v_cache;
+    void *out;                    /* [T, H vdim] */
+    const void *gate;             /* pre-activation of the output gate, [T, >= H vdim], or NULL */
+    int64_t ld_gate;
+    const float *dist_bias;       /* [dist_rows, H] or NULL */
+    int64_t dist_rows;
+    const int64_t *positions;     /* [T] */
+    const int32_t *token_seq;     /* [T] */
+    const int32_t *query_start;   /* [B + 1] */
+    const int32_t *block_tables;  /* [B, max_blocks] */
+    int64_t T, B, max_blocks, H, G, dim, vdim, block_size, window, keep_first;
+    float scale;
+    uint32_t dtype;
+    int32_t max_query_len, max_seq_len;
+} atoma_softmax_attn_args;
+void atoma_softmax_attention_paged(const atoma_softmax_attn_args *args, atoma_stream_t stream);
+
+/* Router with a restricted choice, float32.  z = w_router h over `outputs` router rows (experts, then identity experts);
+ * s = softmax(z) (score_fn 1) or sigmoid(z) (0); choice score c = s + correction (NULL: none).  The outputs form `groups`
+ * equal groups of neighbours (groups <= 1: no restriction); a group's score is its largest c; only outputs of the `keep`
+ * best groups can be chosen (ties: the lower group).  The `top` largest c among them (ties: the lower index) ->
+ * top_expert [T, top] (an index >= the caller's expert count is an identity expert; -1 where fewer than `top` could be
+ * chosen) and top_weight = their s divided by (their sum + 1e-20) (renormalize 1) or as they are (0). */
+void atoma_moe_route_grouped(const void *h, const float *w_router, const float *correction, int32_t *top_expert, float *top_weight,
+                             int64_t T, int64_t width, int64_t outputs, int64_t top, int64_t groups, int64_t keep, int32_t score_fn,
+                             int32_t renormalize, uint32_t dtype, atoma_stream_t stream);
+
+/* atoma_glu_clamped with biases added first: g = gu[t, j] + bias[j], u = gu[t, ff + j] + bias[ff + j] (bias float32 [2 ff]). */
+void atoma_glu_clamped_bias(const void *gu, int64_t ld, const float *bias, void *out, int64_t T, int64_t ff, float limit, float alpha,
+                            float up_shift, uint32_t dtype, atoma_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------ */
 /* Step executor                                                                                */
 /* ------------------------------------------------------------------------------------------ */
-enum { ATOMA_MIXER_SIGMOID_ATTENTION = 0, ATOMA_MIXER_MINGRU = 1, ATOMA_MIXER_LATENT_ATTENTION = 2 };
-enum { ATOMA_BLOCK_SANDWICH = 0, ATOMA_BLOCK_PRENORM = 1 };
+enum { ATOMA_MIXER_SIGMOID_ATTENTION = 0, ATOMA_MIXER_MINGRU = 1, ATOMA_MIXER_LATENT_ATTENTION = 2, ATOMA_MIXER_SOFTMAX_ATTENTION = 3 };
+enum { ATOMA_BLOCK_SANDWICH = 0, ATOMA_BLOCK_PRENORM = 1, ATOMA_BLOCK_LANES = 2 };
+enum { ATOMA_SCORE_SIGMOID = 0, ATOMA_SCORE_SOFTMAX = 1 };
 enum { ATOMA_FF_DENSE = 0, ATOMA_FF_MOE = 1 };
 enum { ATOMA_ACT_SILU = 0, ATOMA_ACT_RELU = 1, ATOMA_ACT_GELU_TANH = 2 };
 
@@ -319,6 +426,19 @@ typedef struct atoma_hybrid_layer {
     int64_t side_part;
     const void *side_gate, *side_proj; /* [side_dim, width], [width, side_dim] */
     const float *side_norm;
+    /* ---- blocks on residual lanes (model.block_style = ATOMA_BLOCK_LANES) ---- */
+    /* softmax attention (uses heads, kv_heads, dim, vdim, scale, window, q_norm / k_norm [dim], k_cache, v_cache, w_o above;
+     * w_qkv = the stacked projections [H dim queries | G dim keys | G vdim values unless values_are_keys | H vdim gate if out_gate]) */
+    int64_t keep_first, dist_rows;
+    const float *dist_bias; /* [dist_rows, heads] or NULL */
+    int32_t values_are_keys, out_gate;
+    /* lane weights of the mixer (1) and the feed-forward (2): read [lanes], write [lanes], mix [lanes, lanes] as [from, to] */
+    const float *lanes_in1, *lanes_out1, *lanes_mix1, *lanes_in2, *lanes_out2, *lanes_mix2;
+    /* feed-forward biases (dense kind; NULL: none) and what the router adds */
+    const float *b_gate_up, *b_down; /* [2 ff], [width] */
+    const float *router_correction;  /* [experts + identity_experts] or NULL */
+    int64_t route_groups, route_keep, identity_experts;
+    int32_t score_fn, scale_input;   /* ATOMA_SCORE_*; 1: the router's weight scales the expert's input, 0: its output */
 } atoma_hybrid_layer;
 
 typedef struct atoma_hybrid_model {
@@ -338,6 +458,9 @@ typedef struct atoma_hybrid_model {
     float logit_softcap;    /* <= 0: none */
     const void *side_table; /* [vocab, side_table_width] */
     int64_t side_dim, side_table_width;
+    /* ---- designs on residual lanes ---- */
+    int32_t lanes;          /* copies of the residual stream (ATOMA_BLOCK_LANES: >= 1) */
+    float embed_scale;      /* the embedding row times this; no position signal is added */
 } atoma_hybrid_model;
 
 typedef struct atoma_hybrid_batch {
@@ -356,14 +479,14 @@ typedef struct atoma_hybrid_batch {
     int64_t scratch_bytes;
     float *logits;                /* out [num_selected, vocab] */
     uint32_t *next_tokens;        /* out [num_selected] greedy */
-    float *residual_trace;        /* optional out [num_layers, T, width]: the residual stream after every layer */
+    float *residual_trace;        /* optional out [num_layers, T, width]: the residual stream (the sum of the lanes) after every layer */
     /* long prompt portions (pre-norm designs; all zero = none): sequences with at least long_min_q tokens in the step, how many
      * there are, the sum of their tokens and of their contexts (tokens already cached) */
     int32_t long_seqs, long_min_q;
     int64_t long_tokens, long_ctx_sum;
 } atoma_hybrid_batch;
 
-int64_t atoma_hybrid_abi_sizeof(int which); /* 0 layer, 1 model, 2 batch, 3 attention args, 4 gated residual args, 5 latent attention args, 6 expert args, 7 expanded attention args */
+int64_t atoma_hybrid_abi_sizeof(int which); /* 0 layer, 1 model, 2 batch, 3 attention args, 4 gated residual args, 5 latent attention args, 6 expert args, 7 expanded attention args, 8 lanes update args, 9 softmax attention args */
 int64_t atoma_hybrid_scratch_bytes(const atoma_hybrid_model *model, int64_t num_tokens, int64_t num_selected);
 void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_hybrid_batch *batch, atoma_stream_t stream);
 
