@@ -119,6 +119,11 @@ def forward(cfg, w, tokens):
     the sum of the lanes after every layer [layers, T, W])."""
     eps = cfg["norm"]["eps"]
     n_lanes = int(cfg.get("streams") or 1)
+    if "streams" not in cfg:        # one residual stream, x <- x + y
+        w = dict(w)
+        for i in range(len(cfg["layers"])):
+            for q in (1, 2):
+                w[f"l{i}.hc{q}.in"], w[f"l{i}.hc{q}.out"], w[f"l{i}.hc{q}.mix"] = torch.ones(1, dtype=F64), torch.ones(1, dtype=F64), torch.ones(1, 1, dtype=F64)
     x0 = embed(tokens, w["embed"], cfg["embedding"]["scale"])
     lanes = [x0.clone() for _ in range(n_lanes)]
     trace = []
@@ -147,3 +152,83 @@ def forward(cfg, w, tokens):
         trace.append(sum(lanes))
     x = rms_norm(sum(lanes), w["final.norm"], eps)
     return x @ w["head"].T, torch.stack(trace)
+
+
+# ---- test inputs ----
+def random_config(width=48, vocab=61, lanes=2, layers=3, heads=4, kv_heads=2, dim=8, scale=0.3, table_rows=10, far=37, window=13, keep=3,
+                  ff=40, limit=0.8, experts=6, identity=2, top=3, groups=4, keep_groups=2, expert_ff=20, shared_ff=12, embed_scale=3.0,
+                  eps=1e-5, kinds=None):
+    """A small configuration in the checkpoint's own format.  kinds: per layer "dense" | "moe" | None (default: alternating)."""
+    kinds = kinds or [("dense", "moe", None)[i % 3] if layers > 2 else ("moe", "dense")[i % 2] for i in range(layers)]
+    out = []
+    for kind in kinds:
+        mask = {}
+        if window:
+            mask["size"] = window
+        if keep:
+            mask["keep_first"] = keep
+        mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": scale, "bias_max": far, "mask": mask, "_rows": table_rows}
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": ff, "limit": limit}
+        elif kind == "moe":
+            mlp = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep_groups}},
+                   "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff} if shared_ff else None}
+        else:
+            mlp = None
+        out.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    cfg = {"architecture": "Nemasun", "vocab": vocab, "width": width, "embedding": {"scale": embed_scale}, "norm": {"eps": eps}, "layers": out}
+    if lanes:
+        cfg["streams"] = lanes
+    return cfg
+
+
+def random_weights(cfg, g):
+    """Random tensors under the checkpoint's names, rounded to what bfloat16 holds (float64)."""
+    W, V, S = cfg["width"], cfg["vocab"], cfg.get("streams")
+
+    def r(*shape, s=1.0):
+        return (torch.randn(*shape, generator=g) * s).to(torch.bfloat16).to(F64)
+
+    def mat(o, i):
+        return r(o, i, s=1.0 / math.sqrt(i))
+
+    w = {"embed": r(V, W, s=0.5), "head": mat(V, W), "final.norm": 1 + r(W, s=0.2)}
+    for i, l in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", l["mixer"]
+        H, G, D = m["heads"], m["kv_heads"], m["dim"]
+        w[p + "norm1"] = 1 + r(W, s=0.2)
+        w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.g"], w[p + "mix.o"] = mat(H * D, W), mat(G * D, W), mat(H * D, W), mat(W, H * D)
+        w[p + "mix.q.norm"], w[p + "mix.k.norm"] = 1 + r(D, s=0.3), 1 + r(D, s=0.3)
+        w[p + "mix.rel"] = r(m["_rows"], H, s=1.5)
+        for q in (1, 2):
+            if S and (q == 1 or l["mlp"] is not None):
+                w[f"{p}hc{q}.in"] = 1.0 / S + r(S, s=0.3)
+                w[f"{p}hc{q}.out"] = 1 + r(S, s=0.3)
+                w[f"{p}hc{q}.mix"] = (torch.eye(S) + torch.randn(S, S, generator=g) * 0.25).to(torch.bfloat16).to(F64)
+        f = l["mlp"]
+        if f is None:
+            continue
+        w[p + "norm2"] = 1 + r(W, s=0.2)
+        q = p + "mlp."
+        if f["kind"] == "dense":
+            n = f["ff"]
+            w[q + "gate"], w[q + "up"], w[q + "down"] = mat(n, W), mat(n, W), mat(W, n)
+            w[q + "gate.b"], w[q + "up.b"], w[q + "down.b"] = r(n, s=0.5), r(n, s=0.5), r(W, s=0.5)
+        else:
+            ro, n = f["router"], f["expert"]["ff"]
+            outs = ro["experts"] + ro.get("identity", 0)
+            w[q + "router"] = r(outs, W, s=2.0 / math.sqrt(W))
+            w[q + "correction"] = r(outs, s=0.15)          # the size of the scores themselves: it changes the choice, and some are negative
+            for k in range(ro["experts"]):
+                w[f"{q}e{k}.gate"], w[f"{q}e{k}.up"], w[f"{q}e{k}.down"] = mat(n, W), mat(n, W), mat(W, n)
+            if f.get("shared"):
+                n = f["shared"]["ff"]
+                w[q + "shared.gate"], w[q + "shared.up"], w[q + "shared.down"] = mat(n, W), mat(n, W), mat(W, n)
+    return {k: v.to(torch.bfloat16).to(F64) for k, v in w.items()}      # sums like 1 + r are rounded once more
+
+
+def checkpoint_config(cfg):
+    """The configuration without the generator's private keys (the table's row count is the tensor's shape)."""
+    out = {k: v for k, v in cfg.items() if k != "layers"}
+    out["layers"] = [{**l, "mixer": {k: v for k, v in l["mixer"].items() if not k.startswith("_")}} for l in cfg["layers"]]
+    return out
