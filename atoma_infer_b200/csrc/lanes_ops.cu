@@ -72,15 +72,27 @@ __global__ void __launch_bounds__(kRowThreads) lanes_read_norm_kernel(const floa
     norm_store<T>(row, width, eps, weight, offset, out + r * width, red);
 }
 
-template <typename T>
+// Four consecutive elements at once (8 bytes of bfloat16, 16 of float32); the caller has checked the alignment.
+__device__ __forceinline__ float4 load4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16 *p) {
+    const uint2 v = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// LC = the number of lanes at compile time (the loops over lanes unroll into registers); LC = 0 takes any number up to
+// kMaxLanes at run time.  VEC = four channels per thread and step (the host checks widths and alignments).
+template <typename T, int LC, bool VEC>
 __global__ void __launch_bounds__(kRowThreads) lanes_update_norm_kernel(const atoma_lanes_update_args a) {
     extern __shared__ float row[];
     __shared__ float red[32], mix_s[kMaxLanes * kMaxLanes], out_s[kMaxLanes], in_s[kMaxLanes], tw_s[kMaxTop];
     __shared__ int64_t erow[kMaxTop];   // >= 0: offset of the pair's expert row; -1: identity expert; -2: nothing
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int LM = LC > 0 ? LC : kMaxLanes;
     const int64_t t = blockIdx.x;
-    const int width = static_cast<int>(a.width), lanes = static_cast<int>(a.lanes), top = a.top_expert ? static_cast<int>(a.top) : 0;
+    const int width = static_cast<int>(a.width), lanes = LC > 0 ? LC : static_cast<int>(a.lanes), top = a.top_expert ? static_cast<int>(a.top) : 0;
     for (int i = threadIdx.x; i < lanes * lanes; i += blockDim.x) mix_s[i] = a.w_mix[i];
     for (int i = threadIdx.x; i < lanes; i += blockDim.x) {
         out_s[i] = a.w_out[i];
@@ -97,33 +109,78 @@ __global__ void __launch_bounds__(kRowThreads) lanes_update_norm_kernel(const at
     const T *hin = a.h_in ? static_cast<const T *>(a.h_in) + t * width : nullptr;
     float *x = a.x + t * lanes * width;
     float *ls = a.lane_sum ? a.lane_sum + t * width : nullptr;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v = y ? to_f(y[c]) : 0.f;
-        if (a.y_bias) v += a.y_bias[c];
-        for (int k = 0; k < top; ++k) {
-            if (erow[k] >= 0) v += to_f(eo[erow[k] + c]);
-            else if (erow[k] == -1 && hin) v = fmaf(tw_s[k], to_f(hin[c]), v);
-        }
-        float old[kMaxLanes];
-#pragma unroll
-        for (int s = 0; s < kMaxLanes; ++s)
-            if (s < lanes) old[s] = x[s * width + c];
-        float u = 0.f, total = 0.f;
-#pragma unroll
-        for (int s2 = 0; s2 < kMaxLanes; ++s2) {
-            if (s2 < lanes) {
-                float nv = 0.f;
-#pragma unroll
-                for (int s = 0; s < kMaxLanes; ++s)
-                    if (s < lanes) nv = fmaf(mix_s[s * lanes + s2], old[s], nv);
-                nv = fmaf(out_s[s2], v, nv);
-                x[s2 * width + c] = nv;
-                u = fmaf(in_s[s2], nv, u);
-                total += nv;
+    constexpr int C = VEC ? 4 : 1;
+    for (int c = C * threadIdx.x; c < width; c += C * blockDim.x) {
+        float v[C];
+        if constexpr (VEC) {
+            float4 v4 = y ? load4(y + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (a.y_bias) {
+                const float4 b4 = load4(a.y_bias + c);
+                v4.x += b4.x, v4.y += b4.y, v4.z += b4.z, v4.w += b4.w;
+            }
+            for (int k = 0; k < top; ++k) {
+                if (erow[k] >= 0) {
+                    const float4 e4 = load4(eo + erow[k] + c);
+                    v4.x += e4.x, v4.y += e4.y, v4.z += e4.z, v4.w += e4.w;
+                } else if (erow[k] == -1 && hin) {
+                    const float4 h4 = load4(hin + c);
+                    v4.x = fmaf(tw_s[k], h4.x, v4.x), v4.y = fmaf(tw_s[k], h4.y, v4.y), v4.z = fmaf(tw_s[k], h4.z, v4.z), v4.w = fmaf(tw_s[k], h4.w, v4.w);
+                }
+            }
+            v[0] = v4.x, v[1] = v4.y, v[2] = v4.z, v[3] = v4.w;
+        } else {
+            v[0] = y ? to_f(y[c]) : 0.f;
+            if (a.y_bias) v[0] += a.y_bias[c];
+            for (int k = 0; k < top; ++k) {
+                if (erow[k] >= 0) v[0] += to_f(eo[erow[k] + c]);
+                else if (erow[k] == -1 && hin) v[0] = fmaf(tw_s[k], to_f(hin[c]), v[0]);
             }
         }
-        row[c] = u;
-        if (ls) ls[c] = total;
+        float old[LM][C];
+#pragma unroll
+        for (int s = 0; s < LM; ++s) {
+            if (s < lanes) {
+                if constexpr (VEC) {
+                    const float4 o4 = load4(x + s * width + c);
+                    old[s][0] = o4.x, old[s][1] = o4.y, old[s][2] = o4.z, old[s][3] = o4.w;
+                } else {
+                    old[s][0] = x[s * width + c];
+                }
+            }
+        }
+        float u[C], total[C];
+#pragma unroll
+        for (int i = 0; i < C; ++i) u[i] = total[i] = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < LM; ++s2) {
+            if (s2 < lanes) {
+                float nv[C];
+#pragma unroll
+                for (int i = 0; i < C; ++i) nv[i] = 0.f;
+#pragma unroll
+                for (int s = 0; s < LM; ++s) {
+                    if (s < lanes) {
+                        const float m = mix_s[s * lanes + s2];
+#pragma unroll
+                        for (int i = 0; i < C; ++i) nv[i] = fmaf(m, old[s][i], nv[i]);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < C; ++i) {
+                    nv[i] = fmaf(out_s[s2], v[i], nv[i]);
+                    u[i] = fmaf(in_s[s2], nv[i], u[i]);
+                    total[i] += nv[i];
+                }
+                if constexpr (VEC) *reinterpret_cast<float4 *>(x + s2 * width + c) = make_float4(nv[0], nv[1], nv[2], nv[3]);
+                else x[s2 * width + c] = nv[0];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < C; ++i) row[c + i] = u[i];
+        if (ls) {
+            if constexpr (VEC) *reinterpret_cast<float4 *>(ls + c) = make_float4(total[0], total[1], total[2], total[3]);
+            else ls[c] = total[0];
+        }
     }
     if (!a.w_next) return;
     __syncthreads();   // every channel of h_in has been read before h (possibly the same buffer) is written
@@ -228,10 +285,33 @@ bool hyb_lanes_update_norm(const atoma_lanes_update_args &a, cudaStream_t stream
     }
     const size_t smem = static_cast<size_t>(a.width) * 4;
     if (!row_fits(smem, "atoma_lanes_update_norm")) return false;
-    HYB_BIG_SMEM(lanes_update_norm_kernel, smem)
-#define CALL(TT) launch_ex(lanes_update_norm_kernel<TT>, dim3(static_cast<unsigned>(a.T)), dim3(kRowThreads), smem, stream, a)
-    return hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "lanes_update_norm_kernel");
-#undef CALL
+    auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool specialised = a.lanes <= 4 || a.lanes == 6 || a.lanes == 8;   // other counts: run-time loops, one channel per thread
+    const bool vec = specialised && a.width % 4 == 0 && al(a.x) && al(a.y) && al(a.y_bias) && al(a.expert_out) && al(a.h_in) && al(a.lane_sum);
+    cudaError_t e;
+#define LANES_CASE(TT, LC)                                                                                                              \
+    {                                                                                                                                   \
+        if (smem > 48 * 1024) {                                                                                                         \
+            cudaFuncSetAttribute(lanes_update_norm_kernel<TT, LC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);      \
+            cudaFuncSetAttribute(lanes_update_norm_kernel<TT, LC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);     \
+        }                                                                                                                               \
+        e = vec ? launch_ex(lanes_update_norm_kernel<TT, LC, true>, dim3(static_cast<unsigned>(a.T)), dim3(kRowThreads), smem, stream, a) \
+                : launch_ex(lanes_update_norm_kernel<TT, LC, false>, dim3(static_cast<unsigned>(a.T)), dim3(kRowThreads), smem, stream, a); \
+    }
+#define LANES_SWITCH(TT)                     \
+    switch (a.lanes) {                       \
+        case 1: LANES_CASE(TT, 1) break;     \
+        case 2: LANES_CASE(TT, 2) break;     \
+        case 3: LANES_CASE(TT, 3) break;     \
+        case 4: LANES_CASE(TT, 4) break;     \
+        case 6: LANES_CASE(TT, 6) break;     \
+        case 8: LANES_CASE(TT, 8) break;     \
+        default: LANES_CASE(TT, 0) break;    \
+    }
+    if (a.dtype == ATOMA_DTYPE_BF16) LANES_SWITCH(__nv_bfloat16) else LANES_SWITCH(float)
+#undef LANES_SWITCH
+#undef LANES_CASE
+    return hybrid::launched(e, "lanes_update_norm_kernel");
 }
 
 bool hyb_qk_headnorm_cache(const void *proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off, const float *q_w, const float *k_w,

@@ -35,6 +35,12 @@ constexpr int kRowsCta = 64;       // query rows per CTA (portions)
 constexpr int kBiasSmem = 2048;    // distances whose bias is kept in shared memory (portions)
 constexpr float kLog2e = 1.4426950408889634f;
 
+__device__ __forceinline__ float ex2(float x) {   // 2^x, flushing; ex2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct TcLayout {
     int k_off, v_off, bias_off, total;
 };
@@ -47,13 +53,15 @@ __host__ __device__ inline TcLayout tc_layout(int D, int DV, int bias_n) {
     return l;
 }
 
-template <int DMAX, bool ROWS_ARE_HEADS>
-__global__ void __launch_bounds__(128) softmax_attn_tc_kernel(const atoma_softmax_attn_args a, int bias_n, int splits, float *__restrict__ partial) {
+// EXACT: dim = vdim = DMAX (the usual case): strides and loop bounds are compile-time constants.
+template <int DMAX, bool ROWS_ARE_HEADS, bool EXACT>
+__global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_softmax_attn_args a, int bias_n, int splits, float *__restrict__ partial) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
     constexpr int NT = ROWS_ARE_HEADS ? 2 : kKeys / 8;   // 8-key score tiles per warp and key tile
-    const int H = static_cast<int>(a.H), G = static_cast<int>(a.G), D = static_cast<int>(a.dim), DV = static_cast<int>(a.vdim);
+    const int H = static_cast<int>(a.H), G = static_cast<int>(a.G);
+    const int D = EXACT ? DMAX : static_cast<int>(a.dim), DV = EXACT ? DMAX : static_cast<int>(a.vdim);
     const int rep = H / G;
     const int b = blockIdx.y;
     const int t_begin = a.query_start[b], n_q = a.query_start[b + 1] - t_begin;
@@ -138,33 +146,50 @@ __global__ void __launch_bounds__(128) softmax_attn_tc_kernel(const atoma_softma
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float scale2 = a.scale * kLog2e;
 
+    // cache rows of a tile's keys, looked up once per key one tile ahead of the copies that use them (-1: past the last key)
+    __shared__ int64_t slot_s[2][kKeys];
+    auto slot_of = [&](int i) -> int64_t {     // thread t < 64: the cache row of key t of tile i
+        if (threadIdx.x >= kKeys) return -1;
+        const int j = tile_of(i) * kKeys + threadIdx.x;
+        return j <= p_last ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : -1;
+    };
+    auto fill_slots = [&](int i, int buf) {
+        const int64_t v = slot_of(i);
+        if (threadIdx.x < kKeys) slot_s[buf][threadIdx.x] = v;
+    };
     const int ck = D / 8, cv = DV / 8;   // 16-byte pieces per cache row of one kv head
-    auto stage_tile = [&](int kt, int st) {
+    const int k_jj0 = threadIdx.x / ck, k_e0 = threadIdx.x % ck, k_djj = 128 / ck, k_de = 128 % ck;
+    const int v_jj0 = threadIdx.x / cv, v_e0 = threadIdx.x % cv, v_djj = 128 / cv, v_de = 128 % cv;
+    auto stage_tile = [&](int buf, int st) {
         __nv_bfloat16 *Kd = Ks0 + st * k_stage, *Vd = Vs0 + st * v_stage;
-        for (int idx = threadIdx.x; idx < kKeys * ck; idx += blockDim.x) {
-            const int jj = idx / ck, e = idx % ck, j = kt * kKeys + jj;
-            const bool ok = j <= p_last;
-            const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
-            cp_async_16(smem_u32(Kd + jj * (D + 8) + e * 8), kc + (slot * G + g) * D + e * 8, ok ? 16 : 0);
+        const int64_t *slots = slot_s[buf];
+        for (int jj = k_jj0, e = k_e0; jj < kKeys;) {     // thread -> pieces threadIdx.x, + 128, ... of the tile, (row, piece) kept incrementally
+            const int64_t slot = slots[jj];
+            cp_async_16(smem_u32(Kd + jj * (D + 8) + e * 8), kc + ((slot < 0 ? 0 : slot) * G + g) * D + e * 8, slot < 0 ? 0 : 16);
+            jj += k_djj, e += k_de;
+            if (e >= ck) e -= ck, ++jj;
         }
-        for (int idx = threadIdx.x; idx < kKeys * cv; idx += blockDim.x) {
-            const int jj = idx / cv, e = idx % cv, j = kt * kKeys + jj;
-            const bool ok = j <= p_last;
-            const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
-            cp_async_16(smem_u32(Vd + jj * (DV + 8) + e * 8), vc + (slot * G + g) * DV + e * 8, ok ? 16 : 0);
+        for (int jj = v_jj0, e = v_e0; jj < kKeys;) {
+            const int64_t slot = slots[jj];
+            cp_async_16(smem_u32(Vd + jj * (DV + 8) + e * 8), vc + ((slot < 0 ? 0 : slot) * G + g) * DV + e * 8, slot < 0 ? 0 : 16);
+            jj += v_djj, e += v_de;
+            if (e >= cv) e -= cv, ++jj;
         }
         cp_async_commit();
     };
-    if (i_begin < i_end) stage_tile(tile_of(i_begin), 0);
-    __syncthreads();   // bias_s
+    if (i_begin < i_end) fill_slots(i_begin, 0);
+    if (i_begin + 1 < i_end) fill_slots(i_begin + 1, 1);
+    __syncthreads();   // bias_s, slot_s
+    if (i_begin < i_end) stage_tile(0, 0);
 
     const int key_off = ROWS_ARE_HEADS ? warp * 16 : 0;   // the warp's keys inside a tile
     const int pw_last = ROWS_ARE_HEADS ? ctx : pw0 + 15;
     const int lo_w = max(0, pw0 - window + 1);
     for (int i = i_begin; i < i_end; ++i) {
         const int st = (i - i_begin) & 1;
+        const int64_t slot_ahead = i + 2 < i_end ? slot_of(i + 2) : -1;   // the block-table read flies during this tile's math
         if (i + 1 < i_end) {
-            stage_tile(tile_of(i + 1), st ^ 1);
+            stage_tile(st ^ 1, st ^ 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             cp_async_wait_all();
@@ -194,21 +219,29 @@ __global__ void __launch_bounds__(128) softmax_attn_tc_kernel(const atoma_softma
             }
             // scale, bias, mask; running maximum per row (rows rq and rq + 8)
             float tmax[2] = {-INFINITY, -INFINITY};
+            // every pair of the warp's rows and keys is visible: below the diagonal for the first row, inside the window of the
+            // last row (or all kept)
+            const bool all_visible = rows_w == 16 && j1 <= pw0 && (pw_last - j0 < window || j1 < keep);
+            const int dist0 = pw0 + rq - j0 - 2 * t4;   // distance of (row rq, key j0 + 2 t4)
 #pragma unroll
             for (int n = 0; n < NT; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int half = e >> 1, row = rq + half * 8;
-                    const int j = j0 + n * 8 + 2 * t4 + (e & 1);
-                    const int p = ROWS_ARE_HEADS ? ctx : pw0 + row;
-                    const int dist = p - j;
-                    float s = -INFINITY;
-                    if (row < rows_w && dist >= 0 && (dist < window || j < keep)) {
-                        s = sacc[n][e] * scale2;
-                        if (a.dist_bias) {
-                            if constexpr (ROWS_ARE_HEADS) s += __ldg(a.dist_bias + static_cast<int64_t>(min(dist, last_row)) * H + h0 + row) * kLog2e;
-                            else s += dist < bias_n ? bias_s[dist] : __ldg(a.dist_bias + static_cast<int64_t>(min(dist, last_row)) * H + h0) * kLog2e;
+                    const int dist = ROWS_ARE_HEADS ? ctx - (j0 + n * 8 + 2 * t4 + (e & 1)) : dist0 + half * 8 - n * 8 - (e & 1);
+                    float s = sacc[n][e] * scale2;
+                    if (a.dist_bias) {
+                        if constexpr (ROWS_ARE_HEADS) {
+                            if (row < rows_w && dist >= 0) s += __ldg(a.dist_bias + static_cast<int64_t>(min(dist, last_row)) * H + h0 + row) * kLog2e;
+                        } else if (bias_n > last_row) {   // the whole table is in shared memory
+                            s += bias_s[min(max(dist, 0), last_row)];
+                        } else if (dist >= 0) {
+                            s += dist < bias_n ? bias_s[dist] : __ldg(a.dist_bias + static_cast<int64_t>(min(dist, last_row)) * H + h0) * kLog2e;
                         }
+                    }
+                    if (!all_visible) {
+                        const int j = (ROWS_ARE_HEADS ? ctx : pw0 + row) - dist;
+                        if (!(row < rows_w && dist >= 0 && (dist < window || j < keep))) s = -INFINITY;
                     }
                     sacc[n][e] = s;
                     tmax[half] = fmaxf(tmax[half], s);
@@ -220,7 +253,7 @@ __global__ void __launch_bounds__(128) softmax_attn_tc_kernel(const atoma_softma
                 tmax[hf] = fmaxf(tmax[hf], __shfl_xor_sync(0xffffffffu, tmax[hf], 2));
                 const float m_new = fmaxf(m_run[hf], tmax[hf]);
                 msub[hf] = m_new == -INFINITY ? 0.f : m_new;          // a row that has seen nothing yet: exp2(-inf - 0) = 0
-                corr[hf] = m_run[hf] == -INFINITY ? 0.f : exp2f(m_run[hf] - msub[hf]);
+                corr[hf] = m_run[hf] == -INFINITY ? 0.f : ex2(m_run[hf] - msub[hf]);
                 m_run[hf] = m_new;
                 l_run[hf] *= corr[hf];
             }
@@ -228,7 +261,7 @@ __global__ void __launch_bounds__(128) softmax_attn_tc_kernel(const atoma_softma
             for (int n = 0; n < NT; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = exp2f(sacc[n][e] - msub[e >> 1]);
+                    const float pv = ex2(sacc[n][e] - msub[e >> 1]);
                     sacc[n][e] = pv;
                     l_run[e >> 1] += pv;
                 }
@@ -258,6 +291,7 @@ __global__ void __launch_bounds__(128) softmax_attn_tc_kernel(const atoma_softma
                 }
             }
         }
+        if (i + 2 < i_end && threadIdx.x < kKeys) slot_s[st][threadIdx.x] = slot_ahead;   // this tile's copies, which read slot_s[st], were issued before the barrier above
         __syncthreads();   // the stage is free for the tile after next
     }
     // row sums: the four lanes of a quad hold disjoint columns
@@ -367,15 +401,20 @@ __global__ void __launch_bounds__(128) softmax_split_merge_kernel(const atoma_so
     }
 }
 
-template <int DMAX, bool ROWS_ARE_HEADS>
-cudaError_t launch_tc(const atoma_softmax_attn_args &a, dim3 grid, size_t smem, int bias_n, int splits, float *partial, cudaStream_t stream) {
+template <int DMAX, bool ROWS_ARE_HEADS, bool EXACT>
+cudaError_t launch_tc_exact(const atoma_softmax_attn_args &a, dim3 grid, size_t smem, int bias_n, int splits, float *partial, cudaStream_t stream) {
     static int attr_dev = -1;
     const int dev = current_device_info().ordinal;
     if (attr_dev != dev) {
-        cudaFuncSetAttribute(softmax_attn_tc_kernel<DMAX, ROWS_ARE_HEADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        cudaFuncSetAttribute(softmax_attn_tc_kernel<DMAX, ROWS_ARE_HEADS, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
         attr_dev = dev;
     }
-    return launch_ex(softmax_attn_tc_kernel<DMAX, ROWS_ARE_HEADS>, grid, dim3(128), smem, stream, a, bias_n, splits, partial);
+    return launch_ex(softmax_attn_tc_kernel<DMAX, ROWS_ARE_HEADS, EXACT>, grid, dim3(128), smem, stream, a, bias_n, splits, partial);
+}
+template <int DMAX, bool ROWS_ARE_HEADS>
+cudaError_t launch_tc(const atoma_softmax_attn_args &a, dim3 grid, size_t smem, int bias_n, int splits, float *partial, cudaStream_t stream) {
+    return (a.dim == DMAX && a.vdim == DMAX) ? launch_tc_exact<DMAX, ROWS_ARE_HEADS, true>(a, grid, smem, bias_n, splits, partial, stream)
+                                             : launch_tc_exact<DMAX, ROWS_ARE_HEADS, false>(a, grid, smem, bias_n, splits, partial, stream);
 }
 
 }  // namespace
@@ -401,9 +440,10 @@ bool hyb_softmax_attention_tc(const atoma_softmax_attn_args &a, cudaStream_t str
         if (a.window > 0) keys = std::min<int64_t>(keys, a.window + std::max<int64_t>(a.keep_first, 0) + kKeys);
         const int64_t tiles = (keys + kKeys - 1) / kKeys;
         const int64_t ctas = a.B * a.G * chunks;
+        // a few CTAs per SM and several waves of them, so that the last wave's idle SMs cost little; at least four tiles per split
         int splits = 1;
-        if (tiles >= 8 && ctas < 2 * current_device_info().sm_count)
-            splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({(2 * current_device_info().sm_count + ctas - 1) / ctas, tiles / 4, 32})));
+        if (tiles >= 8 && ctas < 8 * current_device_info().sm_count)
+            splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({(8 * current_device_info().sm_count + ctas - 1) / ctas, tiles / 4, 32})));
         float *partial = nullptr;
         if (splits > 1) {
             partial = static_cast<float *>(get_workspace(stream, static_cast<size_t>(a.B) * a.H * splits * (DV + 2) * 4, kWorkspaceHybridAttn));
