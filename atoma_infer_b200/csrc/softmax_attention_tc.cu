@@ -146,12 +146,13 @@ __global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_sof
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float scale2 = a.scale * kLog2e;
 
-    // cache rows of a tile's keys, looked up once per key one tile ahead of the copies that use them (-1: past the last key)
+    // cache rows (of the CTA's key/value head) of a tile's keys, looked up once per key one tile ahead of the copies that use
+    // them (-1: past the last key)
     __shared__ int64_t slot_s[2][kKeys];
-    auto slot_of = [&](int i) -> int64_t {     // thread t < 64: the cache row of key t of tile i
+    auto slot_of = [&](int i) -> int64_t {     // thread t < 64: the cache row of key t of tile i, (slot * G + g)
         if (threadIdx.x >= kKeys) return -1;
         const int j = tile_of(i) * kKeys + threadIdx.x;
-        return j <= p_last ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : -1;
+        return j <= p_last ? (static_cast<int64_t>(bt[j / bs]) * bs + j % bs) * G + g : -1;
     };
     auto fill_slots = [&](int i, int buf) {
         const int64_t v = slot_of(i);
@@ -165,13 +166,13 @@ __global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_sof
         const int64_t *slots = slot_s[buf];
         for (int jj = k_jj0, e = k_e0; jj < kKeys;) {     // thread -> pieces threadIdx.x, + 128, ... of the tile, (row, piece) kept incrementally
             const int64_t slot = slots[jj];
-            cp_async_16(smem_u32(Kd + jj * (D + 8) + e * 8), kc + ((slot < 0 ? 0 : slot) * G + g) * D + e * 8, slot < 0 ? 0 : 16);
+            cp_async_16(smem_u32(Kd + jj * (D + 8) + e * 8), kc + (slot < 0 ? 0 : slot) * D + e * 8, slot < 0 ? 0 : 16);
             jj += k_djj, e += k_de;
             if (e >= ck) e -= ck, ++jj;
         }
         for (int jj = v_jj0, e = v_e0; jj < kKeys;) {
             const int64_t slot = slots[jj];
-            cp_async_16(smem_u32(Vd + jj * (DV + 8) + e * 8), vc + ((slot < 0 ? 0 : slot) * G + g) * DV + e * 8, slot < 0 ? 0 : 16);
+            cp_async_16(smem_u32(Vd + jj * (DV + 8) + e * 8), vc + (slot < 0 ? 0 : slot) * DV + e * 8, slot < 0 ? 0 : 16);
             jj += v_djj, e += v_de;
             if (e >= cv) e -= cv, ++jj;
         }
@@ -265,12 +266,14 @@ __global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_sof
                     sacc[n][e] = pv;
                     l_run[e >> 1] += pv;
                 }
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // no row's maximum moved: nothing to rescale
 #pragma unroll
-            for (int n = 0; n < DMAX / 8; ++n) {
-                o[n][0] *= corr[0];
-                o[n][1] *= corr[0];
-                o[n][2] *= corr[1];
-                o[n][3] *= corr[1];
+                for (int n = 0; n < DMAX / 8; ++n) {
+                    o[n][0] *= corr[0];
+                    o[n][1] *= corr[0];
+                    o[n][2] *= corr[1];
+                    o[n][3] *= corr[1];
+                }
             }
 #pragma unroll
             for (int kk = 0; kk < NT / 2; ++kk) {
