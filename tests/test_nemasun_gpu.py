@@ -214,6 +214,8 @@ SHAPES = [  # H, G, dim, vdim, window, keep, table rows, gate
     (5, 5, 16, 16, 1, 2, 4, True),            # a window of one: the token itself and the kept ones
     (32, 1, 16, 16, 9, 1, 7, True),           # more heads per key/value head than a tile has rows
     (2, 2, 128, 128, 100, 4, 12, True),
+    (3, 1, 48, 48, 50, 2, 20, True),          # a head size between the tile sizes
+    (4, 2, 96, 96, 0, 0, 3000, False),        # a table longer than the kernel keeps in shared memory
 ]
 
 
