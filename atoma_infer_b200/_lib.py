@@ -335,6 +335,7 @@ SIGNATURES = {
                              [C.c_void_p] * 3 + [C.c_int64] * 2 + [C.c_uint32, C.c_void_p]),
     "atoma_gate_up_silu": (None, [C.c_void_p] * 3 + [C.c_int64] * 6 + [C.c_uint32, C.c_void_p]),
     "atoma_gate_up_act": (None, [C.c_void_p] * 3 + [C.c_int64] * 6 + [C.c_int32, C.c_uint32, C.c_void_p]),
+    "atoma_gate_up_clamped": (None, [C.c_void_p] * 4 + [C.c_int64] * 6 + [C.c_float] * 3 + [C.c_uint32, C.c_void_p]),
     "atoma_add_rmsnorm": (None, [C.c_void_p] * 5 + [C.c_int64] * 6 + [C.c_float, C.c_uint32, C.c_void_p]),
     "atoma_embedding": (None, [C.c_void_p] * 3 + [C.c_int64] * 5 + [C.c_uint32, C.c_void_p]),
     "atoma_sample_greedy": (None, [C.c_void_p] + [C.c_int64] * 3 + [C.c_uint32] + [C.c_void_p] * 3 +
@@ -394,6 +395,7 @@ SIGNATURES = {
     "atoma_moe_route_grouped": (None, [C.c_void_p] * 5 + [C.c_int64] * 6 + [C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]),
     "atoma_glu_clamped_bias": (None, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_float, C.c_float,
                                       C.c_uint32, C.c_void_p]),
+    "atoma_linear_glu_clamped": (None, [C.c_void_p] * 5 + [C.c_int64] * 3 + [C.c_float] * 3 + [C.c_uint32, C.c_void_p]),
     "atoma_hybrid_abi_sizeof": (C.c_int64, [C.c_int]),
     "atoma_hybrid_scratch_bytes": (C.c_int64, [C.POINTER(HybridModel), C.c_int64, C.c_int64]),
     "atoma_hybrid_step": (None, [C.POINTER(HybridModel), C.POINTER(HybridBatch), C.c_void_p]),

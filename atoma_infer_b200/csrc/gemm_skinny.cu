@@ -272,6 +272,19 @@ __device__ __forceinline__ void epilogue_tile(const SkinnyArgs &a, const EpiRow<
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     float gate;
+                    if (a.glu_act == 3) {   // clamped form with biases (float32 on the rounded projections, as the unfused operator)
+                        float gv = f1[i], uv = f2[i];
+                        if (a.glu_bias && j0 + i < J) {
+                            gv += a.glu_bias[j0 + i];
+                            uv += a.glu_bias[J + j0 + i];
+                        }
+                        if (a.glu_limit > 0.f) {
+                            gv = fminf(gv, a.glu_limit);
+                            uv = fminf(fmaxf(uv, -a.glu_limit), a.glu_limit);
+                        }
+                        o[i] = gv / (1.f + __expf(-a.glu_alpha * gv)) * (uv + a.glu_shift);
+                        continue;
+                    }
                     if (a.glu_act == 1) gate = fmaxf(f1[i], 0.f);
                     else if (a.glu_act == 2) gate = 0.5f * f1[i] * (1.f + tanhf(0.7978845608028654f * (f1[i] + 0.044715f * f1[i] * f1[i] * f1[i])));
                     else gate = f1[i] / (1.f + __expf(-f1[i]));

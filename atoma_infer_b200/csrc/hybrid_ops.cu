@@ -694,6 +694,23 @@ bool hyb_gate_up_act(const void *x, const void *w_gate_up, void *proj, void *act
     return hyb_glu(proj, act_out, T, ff, act, dtype, stream);
 }
 
+bool hyb_glu_clamped_bias(const void *, int64_t, const float *, void *, int64_t, int64_t, float, float, float, uint32_t, cudaStream_t);
+
+// gate/up projection + clamped gated activation with biases: act_out[T, ff] = g sigmoid(alpha g) (u + shift) on the clamped,
+// biased projections; w_gate_up = [Wg; Wu], bias = [bg; bu] (may be null).
+bool hyb_gate_up_clamped(const void *x, const void *w_gate_up, const float *bias, void *proj, void *act_out, int64_t T, int64_t ff, int64_t K,
+                         float limit, float alpha, float shift, uint32_t dtype, cudaStream_t stream) {
+    auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    // decode-sized steps in bfloat16: the activation runs in the projection's epilogue (the tile pairs gate row i with up row i)
+    if (dtype == ATOMA_DTYPE_BF16 && !(g_hybrid_debug & 1) && T <= 128 && K % 64 == 0 && ff % 8 == 0 && al(x) && al(w_gate_up) &&
+        al(act_out) && current_device_info().cc_major == 10) {
+        atoma_gate_up_clamped(x, w_gate_up, bias, act_out, T, ff, K, K, K, ff, limit, alpha, shift, 1, stream);
+        return atoma_last_status() == 0;
+    }
+    if (!hyb_linear(x, w_gate_up, proj, T, 2 * ff, K, dtype, stream)) return false;
+    return hyb_glu_clamped_bias(proj, 2 * ff, bias, act_out, T, ff, limit, alpha, shift, dtype, stream);
+}
+
 bool hyb_scale_greedy(const void *logits, float *out, uint32_t *token_out, int64_t R, int64_t vocab, float scale, float softcap,
                       uint32_t dtype, cudaStream_t stream) {
     if (R <= 0) return true;
@@ -770,3 +787,8 @@ extern "C" void atoma_finish_logits_greedy(const void *logits, float *logits_f32
     hyb_scale_greedy(logits, logits_f32, token_out, R, vocab, scale, softcap, dtype, static_cast<cudaStream_t>(stream));
 }
 extern "C" void atoma_debug_hybrid(int flags) { g_hybrid_debug = flags; }
+extern "C" void atoma_linear_glu_clamped(const void *x, const void *w_gate_up, const float *bias, void *proj, void *act_out, int64_t T,
+                                         int64_t ff, int64_t K, float limit, float alpha, float up_shift, uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    hyb_gate_up_clamped(x, w_gate_up, bias, proj, act_out, T, ff, K, limit, alpha, up_shift, dtype, static_cast<cudaStream_t>(stream));
+}

@@ -59,6 +59,8 @@ bool hyb_qk_headnorm_cache(const void *, int64_t, int64_t, int64_t, int64_t, con
                            void *, int64_t, int64_t, int64_t, int64_t, int64_t, float, uint32_t, cudaStream_t);
 bool hyb_softmax_attention(const atoma_softmax_attn_args &, cudaStream_t);
 bool hyb_glu_clamped_bias(const void *, int64_t, const float *, void *, int64_t, int64_t, float, float, float, uint32_t, cudaStream_t);
+bool hyb_gate_up_clamped(const void *, const void *, const float *, void *, void *, int64_t, int64_t, int64_t, float, float, float, uint32_t,
+                         cudaStream_t);
 int64_t hyb_moe_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t, uint32_t);
 bool hyb_moe_experts(const atoma_moe_args &, const void **, const int32_t **, cudaStream_t);
 
@@ -430,9 +432,8 @@ bool lanes_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, const
     f.lane_sum = lane_sum;
     if (l.ff > 0) {   // the dense feed-forward, or the shared expert of a mixture
         const bool moe = l.ff_kind == ATOMA_FF_MOE;
-        if (!hyb_linear(s.h, moe ? l.w_ff_in : l.w_gate_up, s.proj, T, 2 * l.ff, W, dt, stream)) return false;
-        if (!hyb_glu_clamped_bias(s.proj, 2 * l.ff, moe ? nullptr : l.b_gate_up, s.act, T, l.ff, moe ? l.shared_limit : l.expert_limit,
-                                  l.act_alpha, l.act_up_shift, dt, stream))
+        if (!hyb_gate_up_clamped(s.h, moe ? l.w_ff_in : l.w_gate_up, moe ? nullptr : l.b_gate_up, s.proj, s.act, T, l.ff, W,
+                                 moe ? l.shared_limit : l.expert_limit, l.act_alpha, l.act_up_shift, dt, stream))
             return false;
         if (!hyb_linear(s.act, l.w_down, s.y, T, W, l.ff, dt, stream)) return false;
         f.y = s.y;

@@ -150,7 +150,8 @@ bool qkv_rope_cache(const void *x, const void *wqkv, void *qkv, int64_t T, int64
 }
 
 bool gate_up_silu(const void *x, const void *w, void *y, int64_t T, int64_t inter, int64_t K, int64_t ldx, int64_t ldw,
-                  int64_t ldy, uint32_t dtype, cudaStream_t stream, int act = 0) {
+                  int64_t ldy, uint32_t dtype, cudaStream_t stream, int act = 0, const float *bias = nullptr, float limit = 0.f,
+                  float alpha = 1.f, float shift = 0.f) {
     if (T <= 0 || inter <= 0) return true;
     if (dtype > 1 || !x || !w || !y || !al16(x) || !al16(w) || !al16(y) || ldx % 8 || ldw % 8 || ldy % 8 || ldx < K ||
         ldw < K || ldy < inter || inter % 8) {
@@ -167,6 +168,10 @@ bool gate_up_silu(const void *x, const void *w, void *y, int64_t T, int64_t inte
         SkinnyArgs a{};
         a.epi = kEpiSilu;
         a.glu_act = act;
+        a.glu_bias = bias;
+        a.glu_limit = limit;
+        a.glu_alpha = alpha;
+        a.glu_shift = shift;
         a.y = static_cast<char *>(y) + t0 * ldy * 2;
         a.ldy = ldy;
         if (!launch_skinny_gemm(a, static_cast<const char *>(x) + t0 * ldx * 2, w, tn, K, ldx, ldw, 1,
@@ -296,6 +301,13 @@ extern "C" void atoma_gate_up_act(const void *x, const void *w_gate_up, void *y,
         return;
     }
     gate_up_silu(x, w_gate_up, y, T, inter, K, ldx, ldw, ldy, dtype, static_cast<cudaStream_t>(stream), act);
+}
+
+extern "C" void atoma_gate_up_clamped(const void *x, const void *w_gate_up, const float *bias, void *y, int64_t T, int64_t inter, int64_t K,
+                                      int64_t ldx, int64_t ldw, int64_t ldy, float limit, float alpha, float up_shift, uint32_t dtype,
+                                      atoma_stream_t stream) {
+    clear_status();
+    gate_up_silu(x, w_gate_up, y, T, inter, K, ldx, ldw, ldy, dtype, static_cast<cudaStream_t>(stream), 3, bias, limit, alpha, up_shift);
 }
 
 extern "C" void atoma_add_rmsnorm(const void *x, const void *residual, void *residual_out, const void *weight,

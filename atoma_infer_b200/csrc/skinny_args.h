@@ -30,7 +30,12 @@ struct SkinnyArgs {
     int acc_stride, tmem_cols, nacc;   // TMEM columns between accumulators, allocation, independent accumulators per tile
     int nbuf;                          // accumulator buffers (2: a tile's epilogue overlaps the next tile's MMAs; 1)
     int prefetch_w, is_bf16, epi;
-    int glu_act;                   // kEpiSilu epilogue: gate activation, 0 = silu (Llama), 1 = relu, 2 = gelu (tanh form)
+    int glu_act;                   // kEpiSilu epilogue: gate activation, 0 = silu (Llama), 1 = relu, 2 = gelu (tanh form),
+                                   // 3 = the clamped form below
+    // glu_act 3: g = min(gate + bias[j], limit), u = clamp(up + bias[J + j], -limit, limit) (limit <= 0: no clamp; bias may
+    // be null), y = g sigmoid(alpha g) (u + shift)
+    const float *glu_bias;
+    float glu_limit, glu_alpha, glu_shift;
     int debug_skip;                // diagnostics: 1 = skip x loads, 2 = skip W loads (garbage results)
     int trigger_late;              // 0: release the dependent grid at kernel start; N: N stages before this CTA's last weight load
     unsigned long long *trace;     // diagnostics: [cta][4] globaltimer ns, or null

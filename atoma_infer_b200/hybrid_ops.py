@@ -393,6 +393,17 @@ def glu_clamped_bias(gu, bias, ff, limit, alpha, up_shift):
     return out
 
 
+def linear_glu_clamped(x, w_gate_up, bias, limit, alpha, up_shift):
+    """The clamped gated activation of the projection x w_gate_up^T: one kernel for decode-sized bfloat16 steps."""
+    T, K = x.shape
+    ff = w_gate_up.shape[0] // 2
+    proj = torch.empty((T, 2 * ff), dtype=x.dtype, device=x.device)
+    out = torch.empty((T, ff), dtype=x.dtype, device=x.device)
+    _lib.lib().atoma_linear_glu_clamped(_p(x), _p(w_gate_up), _p(bias), _p(proj), _p(out), T, ff, K, limit, alpha, up_shift, _CODES[x.dtype], _s())
+    _check()
+    return out
+
+
 def moe_expert_rows(h, top_expert, top_weight, w_gate_up, w_down, limit, alpha, up_shift, scale_input=False):
     """The routed experts' result rows as the step executor sees them: (expert_out address, pair_row address, workspace tensor
     that owns both).  For callers that hand them to lanes_update_norm."""

@@ -370,6 +370,12 @@ void atoma_moe_route_grouped(const void *h, const float *w_router, const float *
                              int64_t T, int64_t width, int64_t outputs, int64_t top, int64_t groups, int64_t keep, int32_t score_fn,
                              int32_t renormalize, uint32_t dtype, atoma_stream_t stream);
 
+/* act_out[T, ff] = clamped gated activation (atoma_glu_clamped_bias) of the projection x [T, K] w_gate_up [2 ff, K]^T (gate rows,
+ * then up rows).  Decode-sized bfloat16 steps (T <= 128, K % 64 == 0) run ONE kernel, the activation in the tcgen05 product's
+ * epilogue; everything else atoma_linear into proj [T, 2 ff] and atoma_glu_clamped_bias. */
+void atoma_linear_glu_clamped(const void *x, const void *w_gate_up, const float *bias, void *proj, void *act_out, int64_t T, int64_t ff,
+                              int64_t K, float limit, float alpha, float up_shift, uint32_t dtype, atoma_stream_t stream);
+
 /* atoma_glu_clamped with biases added first: g = gu[t, j] + bias[j], u = gu[t, ff + j] + bias[ff + j] (bias float32 [2 ff]). */
 void atoma_glu_clamped_bias(const void *gu, int64_t ld, const float *bias, void *out, int64_t T, int64_t ff, float limit, float alpha,
                             float up_shift, uint32_t dtype, atoma_stream_t stream);

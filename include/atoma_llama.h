@@ -67,6 +67,12 @@ void atoma_gate_up_silu(const void *x, const void *w_gate_up, void *y, int64_t T
  * 2 = gelu in its tanh form. */
 void atoma_gate_up_act(const void *x, const void *w_gate_up, void *y, int64_t T, int64_t inter, int64_t K,
                        int64_t ldx, int64_t ldw, int64_t ldy, int32_t act, uint32_t dtype, atoma_stream_t stream);
+/* The same kernel with the clamped gated activation in its epilogue: g = min(gate_j + bias[j], limit),
+ * u = clamp(up_j + bias[inter + j], -limit, limit) (limit <= 0: no clamp; bias float32 [2 inter], may be NULL),
+ * y[t, j] = g sigmoid(alpha g) (u + up_shift). */
+void atoma_gate_up_clamped(const void *x, const void *w_gate_up, const float *bias, void *y, int64_t T, int64_t inter, int64_t K,
+                           int64_t ldx, int64_t ldw, int64_t ldy, float limit, float alpha, float up_shift, uint32_t dtype,
+                           atoma_stream_t stream);
 
 /*
  * The MLP of a block (llama.rs:362-366): act[T, inter] = silu(x w_gate^T) * (x w_up^T) and y[T, hidden] = act w_down^T.

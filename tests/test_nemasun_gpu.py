@@ -316,18 +316,27 @@ def test_clamped_activation_with_biases(dtype):
         assert nerr(got, a * no.sigma(1.702 * a) * (b + 1.0)) < tol(dtype, 2e-6, 5e-3)
 
 
-def test_dense_feed_forward_from_its_operators():
+@pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("T,W,ff,limit", [(6, 64, 24, 0.9), (200, 64, 40, 0.5), (33, 128, 72, 0.0), (5, 40, 24, 1.5)])
+def test_dense_feed_forward_from_its_operators(dtype, T, W, ff, limit):
+    """Decode-sized bfloat16 steps run the activation in the projection's epilogue, everything else projection + activation
+    kernel; both against the plain feed-forward, with and without biases."""
     g = torch.Generator().manual_seed(9)
-    T, W, ff, limit = 6, 40, 24, 0.9
     h = bf(torch.randn(T, W, generator=g))
     wg, wu, wd = bf(torch.randn(ff, W, generator=g) / 6), bf(torch.randn(ff, W, generator=g) / 6), bf(torch.randn(W, ff, generator=g) / 5)
     bg, bu, bd = torch.randn(ff, generator=g), torch.randn(ff, generator=g), torch.randn(W, generator=g)
-    gu = _ops().linear(h.to(DEV), torch.cat([wg, wu]).to(DEV))
-    y = _ops().linear(_ops().glu_clamped_bias(gu, torch.cat([bg, bu]).to(DEV), ff, limit, 1.702, 1.0), wd.to(DEV))
+    hd, wgu = h.to(dtype).to(DEV), torch.cat([wg, wu]).to(dtype).to(DEV)
+    a = _ops().linear_glu_clamped(hd, wgu, torch.cat([bg, bu]).to(DEV), limit, 1.702, 1.0)
+    y = _ops().linear(a, wd.to(dtype).to(DEV))
     x = torch.zeros(T, 1, W, device=DEV)
-    _ops().lanes_update_norm(x, y, torch.ones(1, 1, device=DEV), torch.ones(1, device=DEV), torch.float32, y_bias=bd.to(DEV))
-    want = no.clamped_ff(h.double(), wg.double(), bg.double(), wu.double(), bu.double(), wd.double(), bd.double(), limit)
-    assert nerr(x[:, 0], want) < 3e-6
+    _ops().lanes_update_norm(x, y, torch.ones(1, 1, device=DEV), torch.ones(1, device=DEV), dtype, y_bias=bd.to(DEV))
+    lim = limit if limit > 0 else 1e30
+    want = no.clamped_ff(h.double(), wg.double(), bg.double(), wu.double(), bu.double(), wd.double(), bd.double(), lim)
+    assert nerr(x[:, 0], want) < tol(dtype, 3e-6, 1e-2)
+    # no biases, another activation constant: the shared expert's form silu(g) u
+    a = _ops().linear_glu_clamped(hd, wgu, None, 0.0, 1.0, 0.0)
+    gq, uq = h.double() @ wg.double().T, h.double() @ wu.double().T
+    assert nerr(a, gq * no.sigma(gq) * uq) < tol(dtype, 3e-6, 1e-2)
 
 
 @pytest.mark.parametrize("dtype", BOTH)
