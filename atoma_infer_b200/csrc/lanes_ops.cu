@@ -187,43 +187,43 @@ __global__ void __launch_bounds__(kRowThreads) lanes_update_norm_kernel(const at
     norm_store<T>(row, width, a.eps, a.w_next, a.weight_offset, static_cast<T *>(a.h) + t * width, red);
 }
 
-// One warp per (token, head): heads 0 .. H - 1 are queries, H .. H + G - 1 keys (whose raw or separate values ride along).
+// One CTA per token, its warps take the heads in turn: heads 0 .. H - 1 are queries, H .. H + G - 1 keys (whose raw or
+// separate values ride along).
 template <typename T>
-__global__ void __launch_bounds__(128) qk_headnorm_cache_kernel(const T *__restrict__ proj, int64_t ld, int q_off, int k_off, int v_off,
+__global__ void __launch_bounds__(256) qk_headnorm_cache_kernel(const T *__restrict__ proj, int64_t ld, int q_off, int k_off, int v_off,
                                                                 const float *__restrict__ q_w, const float *__restrict__ k_w, float offset,
                                                                 const int64_t *__restrict__ slots, T *__restrict__ q_out,
-                                                                T *__restrict__ k_cache, T *__restrict__ v_cache, int64_t T_, int H, int G,
-                                                                int dim, int vdim, float eps) {
+                                                                T *__restrict__ k_cache, T *__restrict__ v_cache, int H, int G, int dim,
+                                                                int vdim, float eps) {
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int64_t wid = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
-    const int64_t t = wid / (H + G);
-    const int hd = static_cast<int>(wid % (H + G));
-    if (t >= T_) return;
-    const bool is_q = hd < H;
-    const int g = hd - H;
-    const T *src = proj + t * ld + (is_q ? q_off + hd * dim : k_off + g * dim);
-    float ss = 0.f;
-    for (int c = lane; c < dim; c += 32) {
-        const float v = to_f(src[c]);
-        ss = fmaf(v, v, ss);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
-    if (is_q) {
-        T *dst = q_out + (t * H + hd) * dim;
-        for (int c = lane; c < dim; c += 32) dst[c] = from_f<T>(to_f(src[c]) * inv * (offset + q_w[c]));
-        return;
-    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int64_t t = blockIdx.x;
     const int64_t slot = slots ? slots[t] : -1;
-    if (slot < 0) return;
-    T *kd = k_cache + (slot * G + g) * dim;
-    for (int c = lane; c < dim; c += 32) kd[c] = from_f<T>(to_f(src[c]) * inv * (offset + k_w[c]));
-    const T *vs = proj + t * ld + v_off + g * vdim;
-    T *vd = v_cache + (slot * G + g) * vdim;
-    for (int c = lane; c < vdim; c += 32) vd[c] = vs[c];
+    for (int hd = warp; hd < H + G; hd += nwarp) {
+        const bool is_q = hd < H;
+        const int g = hd - H;
+        if (!is_q && slot < 0) continue;
+        const T *src = proj + t * ld + (is_q ? q_off + hd * dim : k_off + g * dim);
+        float ss = 0.f;
+        for (int c = lane; c < dim; c += 32) {
+            const float v = to_f(src[c]);
+            ss = fmaf(v, v, ss);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+        if (is_q) {
+            T *dst = q_out + (t * H + hd) * dim;
+            for (int c = lane; c < dim; c += 32) dst[c] = from_f<T>(to_f(src[c]) * inv * (offset + q_w[c]));
+            continue;
+        }
+        T *kd = k_cache + (slot * G + g) * dim;
+        for (int c = lane; c < dim; c += 32) kd[c] = from_f<T>(to_f(src[c]) * inv * (offset + k_w[c]));
+        const T *vs = proj + t * ld + v_off + g * vdim;
+        T *vd = v_cache + (slot * G + g) * vdim;
+        for (int c = lane; c < vdim; c += 32) vd[c] = vs[c];
+    }
 }
 
 bool row_fits(size_t bytes, const char *what) {
@@ -325,10 +325,10 @@ bool hyb_qk_headnorm_cache(const void *proj, int64_t ld, int64_t q_off, int64_t 
                    static_cast<long long>(G), static_cast<long long>(H));
         return false;
     }
-    const int64_t warps = T * (H + G);
-#define CALL(TT) launch_ex(qk_headnorm_cache_kernel<TT>, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 0, stream, \
+    const unsigned threads = static_cast<unsigned>(std::min<int64_t>(8, H + G) * 32);
+#define CALL(TT) launch_ex(qk_headnorm_cache_kernel<TT>, dim3(static_cast<unsigned>(T)), dim3(threads), 0, stream, \
                            static_cast<const TT *>(proj), ld, static_cast<int>(q_off), static_cast<int>(k_off), static_cast<int>(v_off), q_w, k_w, \
-                           offset, slots, static_cast<TT *>(q_out), static_cast<TT *>(k_cache), static_cast<TT *>(v_cache), T, \
+                           offset, slots, static_cast<TT *>(q_out), static_cast<TT *>(k_cache), static_cast<TT *>(v_cache), \
                            static_cast<int>(H), static_cast<int>(G), static_cast<int>(dim), static_cast<int>(vdim), eps)
     return hybrid::launched(HYB_DISPATCH(dtype, CALL), "qk_headnorm_cache_kernel");
 #undef CALL
