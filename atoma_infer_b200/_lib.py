@@ -227,7 +227,9 @@ class SoftmaxAttnArgs(C.Structure):
                                                                                           ("dist_rows", C.c_int64)] +
                 [(n, C.c_void_p) for n in ("positions", "token_seq", "query_start", "block_tables")] +
                 [(n, C.c_int64) for n in ("T", "B", "max_blocks", "H", "G", "dim", "vdim", "block_size", "window", "keep_first")] +
-                [("scale", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32), ("max_seq_len", C.c_int32)])
+                [("scale", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32), ("max_seq_len", C.c_int32),
+                 ("skip_min_q", C.c_int32), ("long_min_q", C.c_int32), ("long_seqs", C.c_int32), ("long_tokens", C.c_int64),
+                 ("long_ctx_sum", C.c_int64)])
 
 
 class LatentAttnArgs(C.Structure):

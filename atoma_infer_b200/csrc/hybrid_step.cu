@@ -403,6 +403,10 @@ bool lanes_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, const
     a.dtype = dt;
     a.max_query_len = b.max_query_len;
     a.max_seq_len = b.max_seq_len;
+    a.long_min_q = b.long_min_q;
+    a.long_seqs = b.long_seqs;
+    a.long_tokens = b.long_tokens;
+    a.long_ctx_sum = b.long_ctx_sum;
     if (!hyb_softmax_attention(a, stream)) return false;
     if (!hyb_linear(s.act, l.w_o, s.y, T, W, l.heads * l.vdim, dt, stream)) return false;
     atoma_lanes_update_args u{};

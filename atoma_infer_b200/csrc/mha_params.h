@@ -38,6 +38,10 @@ struct MhaParams {
     int window_left;
     int min_len_q;
     const float *sink;
+    // tcgen05 prefill kernel only (null = off): a bias by query-key distance, dist_bias[min(i + shift - j, dist_rows - 1) * dist_heads + head],
+    // added to the scaled score
+    const float *dist_bias;
+    int dist_rows, dist_heads;
 };
 
 }  // namespace atoma

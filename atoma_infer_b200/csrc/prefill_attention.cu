@@ -39,6 +39,7 @@ constexpr int kKvStages = 2;
 constexpr int kTmemCols = 512;   // S_A 0..127 | S_B 128..255 | O_A 256.. | O_B 384..
 constexpr int kPfIssueRegs = 56, kPfSoftmaxRegs = 224;  // setmaxnreg: 168 * 384 = 56 * 128 + 224 * 256
 constexpr float kRescaleThreshold = 8.f;  // log2 units: P <= 2^8 between corrections
+constexpr int kPfBiasSmem = 2048;         // distances whose bias (this head's column of the table) is kept in shared memory
 
 template <int D>
 struct PfCfg {
@@ -75,7 +76,9 @@ __device__ __forceinline__ PfSeq pf_seq(const MhaParams &p, int bidb) {
     return s;
 }
 
-template <typename T, int D>
+// BIASED: a bias by query-key distance is added to the scaled scores (MhaParams::dist_bias); an instantiation of its own, so
+// that the unbiased kernel keeps its register allocation.
+template <typename T, int D, bool BIASED>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const MhaParams p) {
@@ -88,6 +91,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __shared__ __align__(8) uint64_t q_full[kQTiles], k_full[kKvStages], k_empty[kKvStages], v_full[kKvStages],
         v_empty[kKvStages], s_full[kQTiles], p_full[kQTiles], pv_done[kQTiles];
     __shared__ uint32_t tmem_base_smem;
+    __shared__ float bias_s[BIASED ? kPfBiasSmem : 1];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m_block = gridDim.x - 1 - blockIdx.x;  // heaviest (causal) tiles first
@@ -111,6 +115,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
     }
+    const int bias_n = BIASED ? min(p.dist_rows, kPfBiasSmem) : 0;   // a constant table: read before the grid dependency resolves
+    for (int i = tid; i < bias_n; i += kPfThreads) bias_s[i] = p.dist_bias[static_cast<int64_t>(i) * p.dist_heads + blockIdx.y] * 1.4426950408889634f;
     if (warp == 1) tmem_alloc(&tmem_base_smem, kTmemCols);
     tc_fence_before_sync();
     __syncthreads();
@@ -315,6 +321,31 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tmem_s + c * 32, sv_ + c * 32);
                 tmem_ld_wait();
+                // ---- bias by distance: the scores move to the scaled log2 domain here, and `sc` below becomes 1 ----
+                if constexpr (BIASED) {
+                    const int d0 = grow + shift - j * kPfN, last = p.dist_rows - 1;   // distance of this row to the tile's first key
+                    const float sl2 = p.scale_log2;
+                    if (__all_sync(0xffffffffu, d0 - 127 >= last) && last < bias_n) {
+                        // the whole tile lies beyond the table's last row for every row of the warp: one value
+                        const float bv = bias_s[last];
+#pragma unroll
+                        for (int c = 0; c < 128; ++c) sv_[c] = __float_as_uint(fmaf(__uint_as_float(sv_[c]), sl2, bv));
+                    } else if (__all_sync(0xffffffffu, d0 - 127 >= 0 && d0 < bias_n && d0 <= last)) {
+                        // every distance of the tile is a row of the shared-memory copy: no clamps, constant offsets from one address
+                        const float *bp = bias_s + d0;
+#pragma unroll
+                        for (int c = 0; c < 128; ++c) sv_[c] = __float_as_uint(fmaf(__uint_as_float(sv_[c]), sl2, bp[-c]));
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 128; ++c) {
+                            const int dist = min(max(d0 - c, 0), last);
+                            const float bv = dist < bias_n ? bias_s[dist]
+                                                           : __ldg(p.dist_bias + static_cast<int64_t>(dist) * p.dist_heads + head) * 1.4426950408889634f;
+                            sv_[c] = __float_as_uint(fmaf(__uint_as_float(sv_[c]), sl2, bv));
+                        }
+                    }
+                }
+                const float sc = BIASED ? 1.f : p.scale_log2;
                 // ---- masks: only tiles that touch the sequence end or the causal diagonal ----
                 const int col0 = j * kPfN;
                 const bool tail = col0 + kPfN > len_k;
@@ -335,7 +366,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int c = 8; c < 128; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], __uint_as_float(sv_[c]));
                 const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
                                        fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-                const float m_tile = mx * p.scale_log2;  // scale_log2 > 0 (checked on the host)
+                const float m_tile = mx * sc;  // scale_log2 > 0 (checked on the host)
                 // ---- lazy running maximum ----
                 const bool need = m_tile > m_ref + kRescaleThreshold;  // also the first finite tile (m_ref = -inf)
                 if (__any_sync(0xffffffffu, need)) {
@@ -367,8 +398,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(sv_[c * 32 + 2 * i]), p.scale_log2, -m_use));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(sv_[c * 32 + 2 * i + 1]), p.scale_log2, -m_use));
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(sv_[c * 32 + 2 * i]), sc, -m_use));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(sv_[c * 32 + 2 * i + 1]), sc, -m_use));
                         ls[i & 3] += p0 + p1;
                         pk[i] = pack2<T>(p0, p1);
                     }
@@ -463,14 +494,13 @@ bool make_attn_map(CUtensorMap *out, const void *ptr, int d, int heads, int64_t 
     return true;
 }
 
-template <typename T, int D>
-bool launch_prefill(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const MhaParams &p,
-                    cudaStream_t stream) {
+template <typename T, int D, bool BIASED>
+bool launch_prefill_b(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const MhaParams &p, cudaStream_t stream) {
     constexpr size_t smem = PfCfg<D>::kSmem;
     static thread_local int attr_dev = -1;
     const DeviceInfo &di = current_device_info();
     if (attr_dev != di.ordinal) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attn_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(prefill_attn_kernel<T, D, BIASED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem));
         if (e != cudaSuccess) {
             set_status(static_cast<int>(e), "prefill: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -479,9 +509,15 @@ bool launch_prefill(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensor
         attr_dev = di.ordinal;
     }
     dim3 grid((p.seqlen_q + kQTiles * kPfM - 1) / (kQTiles * kPfM), p.h, p.b);
-    prefill_attn_kernel<T, D><<<grid, kPfThreads, smem, stream>>>(mq, mk, mv, p);
+    prefill_attn_kernel<T, D, BIASED><<<grid, kPfThreads, smem, stream>>>(mq, mk, mv, p);
     note_launch();
     return check_launch("prefill_attn_kernel");
+}
+
+template <typename T, int D>
+bool launch_prefill(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const MhaParams &p,
+                    cudaStream_t stream) {
+    return (p.dist_bias && p.dist_rows > 0) ? launch_prefill_b<T, D, true>(mq, mk, mv, p, stream) : launch_prefill_b<T, D, false>(mq, mk, mv, p, stream);
 }
 
 }  // namespace

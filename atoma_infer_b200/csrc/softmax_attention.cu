@@ -8,6 +8,8 @@
 //  * softmax_attn_general_kernel<T>: one CTA per (query token, head), float32 FMA dot products, 128 keys per pass with a
 //    running maximum; the float32 path, and the fallback for head sizes the tiles do not take.
 //  * softmax_attn_tc_kernel (softmax_attention_tc.cu): bfloat16 caches on tensor cores.
+//  * long prompt portions of bfloat16 heads of 64 / 128 (softmax_attention_long.cu): gathered keys and values on the tcgen05
+//    prefill kernel, the kept first tokens merged afterwards.
 // Scores, weights, running maxima and sums are float32; a row's tiles depend on its position and the layer's constants
 // only, never on the batch.
 #include "common.cuh"
@@ -21,6 +23,8 @@ namespace atoma {
 
 extern int g_hybrid_debug;
 bool hyb_softmax_attention_tc(const atoma_softmax_attn_args &a, cudaStream_t stream, bool *taken);   // softmax_attention_tc.cu
+bool hyb_softmax_long_ok(const atoma_softmax_attn_args &a);                                          // softmax_attention_long.cu
+bool hyb_softmax_attention_long(const atoma_softmax_attn_args &a, cudaStream_t stream);
 
 namespace {
 
@@ -51,6 +55,7 @@ __global__ void __launch_bounds__(kGenThreads) softmax_attn_general_kernel(const
     const int H = static_cast<int>(a.H), G = static_cast<int>(a.G), D = static_cast<int>(a.dim), Dv = static_cast<int>(a.vdim);
     const int t = blockIdx.x, h = blockIdx.y, g = h / (H / G);
     const int b = a.token_seq[t];
+    if (a.skip_min_q > 0 && a.query_start && a.query_start[b + 1] - a.query_start[b] >= a.skip_min_q) return;
     const int p = static_cast<int>(a.positions[t]);
     const int bs = static_cast<int>(a.block_size);
     const int32_t *bt = a.block_tables + static_cast<int64_t>(b) * a.max_blocks;
@@ -128,6 +133,16 @@ bool hyb_softmax_attention(const atoma_softmax_attn_args &a, cudaStream_t stream
         (a.gate && a.ld_gate < a.H * a.vdim)) {
         set_status(kErrInvalidArg, "atoma_softmax_attention_paged: null argument, inconsistent head counts, an empty distance table or a gate row shorter than the heads");
         return false;
+    }
+    if (a.skip_min_q == 0 && hyb_softmax_long_ok(a)) {
+        // long portions on the tensor-memory kernel; the step's other sequences (if any) on the kernels below, which skip the long ones
+        if (a.long_seqs < a.B) {
+            atoma_softmax_attn_args rest = a;
+            rest.skip_min_q = a.long_min_q;
+            rest.long_seqs = 0;
+            if (!hyb_softmax_attention(rest, stream)) return false;
+        }
+        return hyb_softmax_attention_long(a, stream);
     }
     if (!(g_hybrid_debug & 2)) {
         bool taken = false;

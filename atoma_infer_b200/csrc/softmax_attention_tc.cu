@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_sof
     const int b = blockIdx.y;
     const int t_begin = a.query_start[b], n_q = a.query_start[b + 1] - t_begin;
     if (ROWS_ARE_HEADS ? n_q != 1 : n_q <= 1) return;   // single tokens are served by the rows-are-heads mapping
+    if (a.skip_min_q > 0 && n_q >= a.skip_min_q) return;   // long portions are served elsewhere
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t4 = lane & 3, rq = lane >> 2;
     const int ctx = static_cast<int>(a.positions[t_begin]);
     // rows of this CTA / warp

@@ -46,7 +46,8 @@ from .scheduler import StepPlan
 from .worker import InputStager, SequenceInput
 
 MIXER_ATTENTION, MIXER_MINGRU, MIXER_LATENT, MIXER_SOFTMAX = 0, 1, 2, 3
-LONG_PORTION = 128        # tokens of a sequence in one step from which latent attention runs on expanded keys and values
+LONG_PORTION = 128        # tokens of a sequence in one step from which attention runs on the tensor-memory prefill kernel
+                          # (latent attention: on expanded keys and values; softmax attention: on gathered ones)
 BLOCK_STYLES = {"sandwich": 0, "prenorm": 1, "lanes": 2}
 SCORE_FNS = {"sigmoid": 0, "softmax": 1}
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
@@ -505,7 +506,7 @@ class HybridExecutor:
         hb.num_tokens, hb.num_seqs, hb.num_selected, hb.max_blocks = T, B, S, bt.shape[1]
         hb.max_query_len = max(c.count for c in chunks)
         hb.max_seq_len = max(c.start + c.count for c in chunks)
-        if self.spec.block_style == "prenorm":
+        if self.spec.block_style in ("prenorm", "lanes"):
             long_ = [c for c in chunks if c.count >= LONG_PORTION]
             hb.long_seqs, hb.long_min_q = len(long_), LONG_PORTION
             hb.long_tokens, hb.long_ctx_sum = sum(c.count for c in long_), sum(c.start for c in long_)

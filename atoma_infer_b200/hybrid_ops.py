@@ -351,7 +351,9 @@ def qk_headnorm_cache(proj, q_off, k_off, v_off, q_w, k_w, offset, slots, k_cach
 
 
 def softmax_attention_paged(q, k_cache, v_cache, positions, token_seq, block_tables, H, G, dim, vdim, block_size, scale, window=0,
-                            keep_first=0, dist_bias=None, gate=None, max_query_len=None, query_start=None, max_seq_len=None):
+                            keep_first=0, dist_bias=None, gate=None, max_query_len=None, query_start=None, max_seq_len=None, long_min_q=0, long_stats=None):
+    """long_min_q > 0: sequences with at least that many tokens in the step take the long-portion path (where the shapes allow);
+    long_stats = (how many such sequences, the sum of their tokens, the sum of their contexts) saves the host reads that find them."""
     from ._lib import SoftmaxAttnArgs
     T = q.shape[0]
     if query_start is None:
@@ -370,6 +372,14 @@ def softmax_attention_paged(q, k_cache, v_cache, positions, token_seq, block_tab
     a.T, a.B, a.max_blocks, a.H, a.G, a.dim, a.vdim = T, block_tables.shape[0], block_tables.shape[1], H, G, dim, vdim
     a.block_size, a.window, a.keep_first, a.scale, a.dtype = block_size, window, keep_first, scale, _CODES[q.dtype]
     a.max_query_len, a.max_seq_len = int(max_query_len), int(max_seq_len)
+    if long_min_q > 0 and long_stats is not None:
+        a.long_min_q, (a.long_seqs, a.long_tokens, a.long_ctx_sum) = long_min_q, long_stats
+    elif long_min_q > 0:
+        qs = query_start.cpu().tolist()
+        ctx = [int(positions[qs[b]]) for b in range(len(qs) - 1)]
+        long_ = [b for b in range(len(qs) - 1) if qs[b + 1] - qs[b] >= long_min_q]
+        a.long_min_q, a.long_seqs = long_min_q, len(long_)
+        a.long_tokens, a.long_ctx_sum = sum(qs[b + 1] - qs[b] for b in long_), sum(ctx[b] for b in long_)
     _lib.lib().atoma_softmax_attention_paged(C.byref(a), _s())
     _check()
     return out

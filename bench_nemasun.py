@@ -93,6 +93,10 @@ def _kernel_rows(torch, s, dev, steps, warmup, hbm, tf):
     f = lambda: ho.softmax_attention_paged(q, kc, vc, pos, tseq, bt, H, G, D, D, page, scale, window=win, keep_first=keep, dist_bias=table,
                                            gate=gate, max_query_len=S, query_start=qs, max_seq_len=S)
     pairs = sum(min(i + 1, win) + min(keep, max(0, i + 1 - win)) for i in range(S))
+    rows["softmax_attention_prefill_short_portions"] = _row(_time(torch, f, steps, warmup, flush), flops=4.0 * H * D * pairs, tf=tf)
+    # the same prompt as a long portion (what portions of 128 tokens and more run): gather + tensor-memory kernel + kept-token merge and gate
+    f = lambda: ho.softmax_attention_paged(q, kc, vc, pos, tseq, bt, H, G, D, D, page, scale, window=win, keep_first=keep, dist_bias=table,
+                                           gate=gate, max_query_len=S, query_start=qs, max_seq_len=S, long_min_q=128, long_stats=(1, S, 0))
     rows["softmax_attention_prefill"] = _row(_time(torch, f, steps, warmup, flush), flops=4.0 * H * D * pairs, tf=tf)
     q3 = torch.randn((S, H, D), device=dev, dtype=bf)
     k3, v3 = torch.randn((S, G, D), device=dev, dtype=bf), torch.randn((S, G, D), device=dev, dtype=bf)

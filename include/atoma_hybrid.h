@@ -357,6 +357,14 @@ typedef struct atoma_softmax_attn_args {
     float scale;
     uint32_t dtype;
     int32_t max_query_len, max_seq_len;
+    int32_t skip_min_q;           /* > 0: sequences with at least this many query tokens in the step are left alone */
+    /* long prompt portions (all zero = none): sequences with at least long_min_q (>= 32) tokens in the step, how many there are,
+     * the sum of their tokens and of their contexts.  bfloat16 heads of 64 or 128 with dim = vdim run them on the tensor-memory
+     * prefill kernel: the keys and values their queries can see through the window are gathered from the pages, the distance
+     * term is added inside that kernel's softmax, the kept first tokens behind the window are a second short pass merged through
+     * the log-sum-exp, and the gate is applied in the merge. */
+    int32_t long_min_q, long_seqs;
+    int64_t long_tokens, long_ctx_sum;
 } atoma_softmax_attn_args;
 void atoma_softmax_attention_paged(const atoma_softmax_attn_args *args, atoma_stream_t stream);
 

@@ -63,12 +63,12 @@ def attention(h, w_q, w_k, w_g, w_o, q_norm, k_norm, table, heads, kv_heads, dim
     rows = table.shape[0]
     out = torch.zeros(T, heads, dim, dtype=F64)
     for i in range(T):
-        js = [j for j in range(i + 1) if visible(i, j, window, keep)]
+        js = torch.tensor([j for j in range(i + 1) if visible(i, j, window, keep)])
+        rows_of = torch.tensor([distance_bucket(i - int(j), rows, far) for j in js])
         for hd in range(heads):
             g = hd // rep
-            s = torch.stack([(q[i, hd] @ k[j, g]) * scale + table[distance_bucket(i - j, rows, far), hd] for j in js])
-            p = torch.softmax(s, 0)
-            out[i, hd] = sum(p[n] * v[j, g] for n, j in enumerate(js))
+            s = (k[js, g] @ q[i, hd]) * scale + table[rows_of, hd]
+            out[i, hd] = torch.softmax(s, 0) @ v[js, g]
     gate = sigma(h @ w_g.T)
     return (out.reshape(T, heads * dim) * gate) @ w_o.T
 

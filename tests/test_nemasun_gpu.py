@@ -149,12 +149,13 @@ def test_per_head_norms_and_cache_write(dtype, H, G, dim, vdim, same):
 def attention_plain(q, k, v, table, scale, window, keep, i, rep):
     """q [H, dim] of position i; k, v [L, G, .] of positions 0 .. L - 1; table [distances, H] or None -> [H, vdim]"""
     H = q.shape[0]
-    js = [j for j in range(i + 1) if no.visible(i, j, window or (1 << 60), keep)]
+    js = torch.tensor([j for j in range(i + 1) if no.visible(i, j, window or (1 << 60), keep)])
     out = []
     for h in range(H):
-        s = torch.stack([(q[h] @ k[j, h // rep]) * scale + (table[min(i - j, table.shape[0] - 1), h] if table is not None else 0.0) for j in js])
-        p = torch.softmax(s, 0)
-        out.append(sum(p[n] * v[j, h // rep] for n, j in enumerate(js)))
+        s = (k[js, h // rep] @ q[h]) * scale
+        if table is not None:
+            s = s + table[torch.clamp(i - js, max=table.shape[0] - 1), h]
+        out.append(torch.softmax(s, 0) @ v[js, h // rep])
     return torch.stack(out)
 
 
@@ -182,7 +183,7 @@ def paged_kv(g, seqs, G, dim, vdim, bs, dtype, extra_pages=3):
             torch.tensor(tseq, dtype=torch.int32, device=DEV), ks, vs)
 
 
-def attention_case(g, dtype, seqs, H, G, dim, vdim, window, keep, rows, gate, general, bs=8, scale=0.35):
+def attention_case(g, dtype, seqs, H, G, dim, vdim, window, keep, rows, gate, general, bs=8, scale=0.35, long_min_q=0):
     kc, vc, bt, pos, tseq, ks, vs = paged_kv(g, seqs, G, dim, vdim, bs, dtype)
     T = pos.numel()
     q = bf(torch.randn(T, H * dim, generator=g))
@@ -192,7 +193,7 @@ def attention_case(g, dtype, seqs, H, G, dim, vdim, window, keep, rows, gate, ge
         _ops().debug_flags(2)
     got = _ops().softmax_attention_paged(q.to(dtype).to(DEV), kc, vc, pos, tseq, bt, H, G, dim, vdim, bs, scale, window=window, keep_first=keep,
                                          dist_bias=table.to(DEV) if rows else None,
-                                         gate=gt.to(dtype).to(DEV)[:, 8:] if gate else None)
+                                         gate=gt.to(dtype).to(DEV)[:, 8:] if gate else None, long_min_q=long_min_q)
     want, t = [], 0
     for b, (ctx, n) in enumerate(seqs):
         for i in range(ctx, ctx + n):
@@ -228,6 +229,24 @@ def test_attention_on_a_mixed_batch(dtype, general, H, G, dim, vdim, window, kee
     seqs = [(0, 37), (90, 1), (21, 70), (0, 1), (140, 3), (7, 1), (200, 1)]
     got, want = attention_case(g, dtype, seqs, H, G, dim, vdim, window, keep, rows, gate, general)
     assert nerr(got, want) < tol(dtype, 3e-6, 1.5e-2)
+
+
+@pytest.mark.parametrize("H,G,dim,window,keep,rows,gate", [(4, 2, 64, 0, 0, 40, True), (2, 1, 128, 100, 5, 30, True), (4, 2, 64, 150, 70, 3000, False),
+                                                        (3, 1, 128, 129, 200, 12, True), (2, 2, 64, 1, 3, 5, True)])
+def test_long_portions_on_the_tensor_memory_kernel(H, G, dim, window, keep, rows, gate):
+    """Portions of 128 tokens and more (bfloat16 heads of 64 / 128) run on gathered keys and values with the kept first tokens
+    merged afterwards; shorter portions and single tokens of the same step run on the other kernels."""
+    g = torch.Generator().manual_seed(12)
+    seqs = [(0, 140), (90, 1), (77, 130), (0, 40), (200, 129), (5, 127)]
+    got, want = attention_case(g, torch.bfloat16, seqs, H, G, dim, dim, window, keep, rows, gate, False, bs=16, scale=dim ** -0.5, long_min_q=128)
+    t = 0
+    for ctx, n in seqs:       # per sequence, so that a long one's error cannot hide among the others
+        assert nerr(got[t:t + n], want[t:t + n]) < 1.5e-2, (ctx, n)
+        t += n
+    # only long sequences in the step
+    got, want = attention_case(g, torch.bfloat16, [(0, 130), (64, 128)], H, G, dim, dim, window, keep, rows, gate, False, bs=16, scale=dim ** -0.5,
+                               long_min_q=128)
+    assert nerr(got, want) < 1.5e-2
 
 
 @pytest.mark.parametrize("dtype", BOTH)
@@ -453,6 +472,30 @@ def test_decoding_token_by_token_equals_the_whole_prompt(tmp_path, name):
     eng = make_engine(tmp_path, cfg, w, torch.float32, max_tokens=128, block_size=4)
     got = [eng.step_forced([("a", [t], [0])]).logits.clone() for t in toks]
     assert nerr(torch.cat(got), want) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", BOTH)
+def test_long_portions_beside_decoded_tokens(tmp_path, dtype):
+    """Portions of 128 tokens and more (bfloat16: the tensor-memory kernel) in one step with short portions and single tokens,
+    over a window that the long portions cross and kept tokens that fall behind it."""
+    cfg, w, g = build("heads_of_64", 8)
+    toks = {k: torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for k, n in (("a", 400), ("b", 40), ("c", 330))}
+    want = {k: no.forward(cfg, w, t)[0] for k, t in toks.items()}
+    eng = make_engine(tmp_path, cfg, w, dtype, max_tokens=1024)
+    steps = [[("a", 200), ("b", 3)], [("a", 130), ("b", 1), ("c", 129)], [("c", 200), ("a", 69), ("b", 36)], [("a", 1), ("c", 1)]]
+    at, got = {k: 0 for k in toks}, {k: [] for k in toks}
+    for step in steps:
+        entries = []
+        for k, n in step:
+            entries.append((k, toks[k][at[k]:at[k] + n], list(range(n))))
+            at[k] += n
+        out = eng.step_forced(entries)
+        r = 0
+        for k, n in step:
+            got[k].append(out.logits[r:r + n].clone())
+            r += n
+    for k in toks:
+        assert at[k] == len(toks[k]) and model_close(torch.cat(got[k]), want[k], dtype), k
 
 
 def test_long_decoding_far_past_the_window(tmp_path):
