@@ -16,8 +16,8 @@
 // its position and the layer's constants only.
 //
 // Why mma.sync and not tcgen05: the single-token mapping has at most 16 useful rows (a 128-row tensor-memory tile would be
-// 7/8 padding) and is bound by the cache stream; the portion mapping shares this file's softmax and mask code so that both
-// evaluate the same expressions.
+// 7/8 padding) and is bound by the cache stream; portions of 128 tokens and more in the shapes the tensor-memory prefill
+// kernel takes run there (softmax_attention_long.cu), so this file's portion mapping serves the short ones and the other shapes.
 #include "common.cuh"
 #include "hybrid_common.cuh"
 
