@@ -186,7 +186,18 @@ class HybridLayer(C.Structure):
                 [(n, C.c_void_p) for n in ("lanes_in1", "lanes_out1", "lanes_mix1", "lanes_in2", "lanes_out2", "lanes_mix2",
                                            "b_gate_up", "b_down", "router_correction")] +
                 [(n, C.c_int64) for n in ("route_groups", "route_keep", "identity_experts")] +
-                [("score_fn", C.c_int32), ("scale_input", C.c_int32)])
+                [("score_fn", C.c_int32), ("scale_input", C.c_int32)] +
+                # parallel blocks: what precedes the layer, tap filters, the layer's state row, the stacked projection's columns,
+                # gated linear attention, the pair of mixers (rotary sigmoid attention + gated delta rule), rotated latent keys
+                [("add_embedding", C.c_int32), ("add_vec", C.c_void_p), ("taps", C.c_int64), ("tap_w1", C.c_void_p), ("tap_w2", C.c_void_p),
+                 ("layer_state", C.c_void_p), ("layer_state_stride", C.c_int64), ("proj_cols", C.c_int64)] +
+                [(n, C.c_int64) for n in ("q_off", "k_off", "v_off", "g_off", "a_off", "a_rank")] +
+                [(n, C.c_void_p) for n in ("w_a2", "a2_bias", "head_norm")] + [("tau", C.c_float)] +
+                [("qk_freq", C.c_void_p), ("v_freq", C.c_void_p), ("rot_pairs", C.c_int64), ("v_pairs", C.c_int64), ("rot_interleaved", C.c_int32)] +
+                [(n, C.c_int64) for n in ("r_heads", "r_kv_heads", "r_dim", "r_vdim", "r_taps", "rq_off", "rk_off", "rv_off", "rg_off", "rb_off",
+                                          "ra_off")] +
+                [(n, C.c_void_p) for n in ("r_tap_w", "r_a_log", "r_dt_bias", "r_head_norm", "r_w_o", "out_norm_a", "out_norm_b")] +
+                [("rot_dim", C.c_int64)])
 
 
 class HybridModel(C.Structure):
@@ -230,6 +241,46 @@ class SoftmaxAttnArgs(C.Structure):
                 [("scale", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32), ("max_seq_len", C.c_int32),
                  ("skip_min_q", C.c_int32), ("long_min_q", C.c_int32), ("long_seqs", C.c_int32), ("long_tokens", C.c_int64),
                  ("long_ctx_sum", C.c_int64)])
+
+
+class ParallelResidualArgs(C.Structure):
+    """struct atoma_parallel_residual_args"""
+
+    _fields_ = ([(n, C.c_void_p) for n in ("y_a", "y_b", "y_ff", "norm_a", "norm_b")] + [("mix_scale", C.c_float)] +
+                [(n, C.c_void_p) for n in ("x", "trace", "add_rows", "add_vec", "w_next", "h")] +
+                [("T", C.c_int64), ("width", C.c_int64), ("eps", C.c_float), ("weight_offset", C.c_float), ("dtype", C.c_uint32)])
+
+
+class TapFilterArgs(C.Structure):
+    """struct atoma_tap_filter_args"""
+
+    _fields_ = ([("in_", C.c_void_p), ("ld_in", C.c_int64)] + [(n, C.c_void_p) for n in ("w1", "w2", "out1", "out2")] +
+                [("ld_out", C.c_int64), ("history", C.c_void_p), ("history_stride", C.c_int64)] +
+                [(n, C.c_void_p) for n in ("state_slots", "token_seq", "query_start", "context_lens")] +
+                [(n, C.c_int64) for n in ("T", "B", "channels", "taps")] +
+                [("residual", C.c_int32), ("act", C.c_int32), ("dtype", C.c_uint32)])
+
+
+class StateScanArgs(C.Structure):
+    """struct atoma_state_scan_args"""
+
+    _fields_ = ([("kind", C.c_int32)] + [(n, C.c_void_p) for n in ("q", "k", "v", "z", "b_pre", "a_pre")] +
+                [(n, C.c_int64) for n in ("ld_q", "ld_k", "ld_v", "ld_z", "ld_b", "ld_a")] +
+                [(n, C.c_void_p) for n in ("z_bias", "a_log", "dt_bias")] +
+                [(n, C.c_float) for n in ("tau", "q_scale", "unit_eps")] +
+                [("state", C.c_void_p), ("state_stride", C.c_int64)] +
+                [(n, C.c_void_p) for n in ("state_slots", "query_start", "context_lens", "out")] +
+                [(n, C.c_int64) for n in ("T", "B", "H", "G", "dim", "vdim")] + [("dtype", C.c_uint32)])
+
+
+class QkvRopeArgs(C.Structure):
+    """struct atoma_qkv_rope_args"""
+
+    _fields_ = ([("proj", C.c_void_p)] + [(n, C.c_int64) for n in ("ld", "q_off", "k_off", "v_off")] +
+                [(n, C.c_void_p) for n in ("q_weight", "k_weight", "qk_freq", "v_freq")] +
+                [("rot_pairs", C.c_int64), ("v_pairs", C.c_int64), ("interleaved", C.c_int32)] +
+                [(n, C.c_void_p) for n in ("positions", "slot_mapping", "q_out", "k_cache", "v_cache")] +
+                [(n, C.c_int64) for n in ("T", "H", "G", "dim", "vdim")] + [("eps", C.c_float), ("dtype", C.c_uint32)])
 
 
 class LatentAttnArgs(C.Structure):
@@ -398,6 +449,17 @@ SIGNATURES = {
     "atoma_glu_clamped_bias": (None, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_float, C.c_float,
                                       C.c_uint32, C.c_void_p]),
     "atoma_linear_glu_clamped": (None, [C.c_void_p] * 5 + [C.c_int64] * 3 + [C.c_float] * 3 + [C.c_uint32, C.c_void_p]),
+    "atoma_parallel_residual_norm": (None, [C.POINTER(ParallelResidualArgs), C.c_void_p]),
+    "atoma_tap_filter": (None, [C.POINTER(TapFilterArgs), C.c_void_p]),
+    "atoma_state_scan": (None, [C.POINTER(StateScanArgs), C.c_void_p]),
+    "atoma_headnorm_gate": (None, [C.c_void_p] * 3 + [C.c_int64, C.c_void_p] + [C.c_int64] * 3 + [C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_qkv_headnorm_rope_cache": (None, [C.POINTER(QkvRopeArgs), C.c_void_p]),
+    "atoma_rotate_heads": (None, [C.c_void_p] * 3 + [C.c_int64] * 4 + [C.c_int32, C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_latent_norm_rope_cache": (None, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32] + [C.c_void_p] * 4 +
+                                     [C.c_int64] * 4 + [C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_latent_query_absorb_rope": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p] + [C.c_int64] * 5 +
+                                       [C.c_uint32, C.c_void_p]),
+    "atoma_latent_expand_values": (None, [C.c_void_p] * 3 + [C.c_int64] * 5 + [C.c_uint32, C.c_void_p]),
     "atoma_hybrid_abi_sizeof": (C.c_int64, [C.c_int]),
     "atoma_hybrid_scratch_bytes": (C.c_int64, [C.POINTER(HybridModel), C.c_int64, C.c_int64]),
     "atoma_hybrid_step": (None, [C.POINTER(HybridModel), C.POINTER(HybridBatch), C.c_void_p]),

@@ -61,6 +61,17 @@ bool hyb_softmax_attention(const atoma_softmax_attn_args &, cudaStream_t);
 bool hyb_glu_clamped_bias(const void *, int64_t, const float *, void *, int64_t, int64_t, float, float, float, uint32_t, cudaStream_t);
 bool hyb_gate_up_clamped(const void *, const void *, const float *, void *, void *, int64_t, int64_t, int64_t, float, float, float, uint32_t,
                          cudaStream_t);
+bool hyb_parallel_residual_norm(const atoma_parallel_residual_args &, cudaStream_t);
+bool hyb_tap_filter(const atoma_tap_filter_args &, cudaStream_t);
+bool hyb_state_scan(const atoma_state_scan_args &, cudaStream_t);
+bool hyb_headnorm_gate(const float *, const float *, const void *, int64_t, void *, int64_t, int64_t, int64_t, float, uint32_t, cudaStream_t);
+bool hyb_qkv_headnorm_rope_cache(const atoma_qkv_rope_args &, cudaStream_t);
+bool hyb_rotate_heads(void *, const int64_t *, const float *, int64_t, int64_t, int64_t, int64_t, int32_t, float, uint32_t, cudaStream_t);
+bool hyb_latent_norm_rope_cache(const void *, int64_t, const float *, const float *, const float *, int64_t, int32_t, const int64_t *,
+                                const int64_t *, void *, void *, int64_t, int64_t, int64_t, int64_t, float, uint32_t, cudaStream_t);
+bool hyb_latent_query_absorb_rope(const void *, const void *, const float *, int64_t, int32_t, const int64_t *, float *, int64_t, int64_t, int64_t,
+                                  int64_t, int64_t, uint32_t, cudaStream_t);
+bool hyb_latent_expand_values(const float *, const void *, void *, int64_t, int64_t, int64_t, int64_t, int64_t, uint32_t, cudaStream_t);
 int64_t hyb_moe_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t, uint32_t);
 bool hyb_moe_experts(const atoma_moe_args &, const void **, const int32_t **, cudaStream_t);
 
@@ -72,6 +83,8 @@ struct Widths {
     int64_t proj = 0, q = 0, act = 0;   // widest projection output, query row, mixer / feed-forward activation row
     int64_t cq = 0, lat = 0, route = 0, side = 0;   // query latent row, heads x latent row, router outputs per token, side input row
     int64_t moe = 0;                    // bytes of the routed experts' workspace
+    int64_t conv = 0, of32 = 0;         // parallel blocks: filtered q / k / v row of a delta-rule mixer, float32 read-out row of a recurrence
+    bool parallel = false, keep_embedding = false;
 };
 
 inline bool gated(const float *bias) { return bias != nullptr; }
@@ -85,6 +98,32 @@ Widths widths(const atoma_hybrid_model &m, int64_t T) {
     Widths w;
     for (int64_t i = 0; i < m.num_layers; ++i) {
         const atoma_hybrid_layer &l = m.layers[i];
+        if (m.block_style == ATOMA_BLOCK_PARALLEL) {
+            w.parallel = true;
+            w.keep_embedding = w.keep_embedding || l.add_embedding;
+            w.proj = std::max(w.proj, l.proj_cols);
+            if (l.has_mlp) {
+                w.proj = std::max(w.proj, 2 * l.ff);
+                w.act = std::max(w.act, l.ff);
+            }
+            if (l.mixer == ATOMA_MIXER_GLA) {
+                w.q = std::max(w.q, l.heads * l.dim);
+                w.cq = std::max(w.cq, l.a_rank);
+                w.act = std::max(w.act, l.heads * l.vdim);
+                w.of32 = std::max(w.of32, l.heads * l.vdim);
+            } else if (l.mixer == ATOMA_MIXER_LATENT_ATTENTION) {
+                w.q = std::max(w.q, l.heads * (l.dim + l.rot_dim));
+                w.cq = std::max(w.cq, l.q_rank);
+                w.act = std::max(w.act, l.heads * l.vdim);
+                w.lat = std::max(w.lat, l.heads * (l.kv_rank + l.rot_dim));
+            } else if (l.mixer == ATOMA_MIXER_PAIR) {
+                w.q = std::max(w.q, l.heads * l.dim);
+                w.act = std::max(w.act, std::max(l.heads * l.vdim, l.r_heads * l.r_vdim));
+                w.conv = std::max(w.conv, 2 * l.r_kv_heads * l.r_dim + l.r_heads * l.r_vdim);
+                w.of32 = std::max(w.of32, l.r_heads * l.r_vdim);
+            }
+            continue;
+        }
         if (l.mixer == ATOMA_MIXER_LATENT_ATTENTION) {
             w.proj = std::max(w.proj, l.q_rank + l.kv_rank + (gated(l.gate1_bias) ? m.width : 0));
             w.q = std::max(w.q, l.heads * l.dim);
@@ -140,6 +179,9 @@ struct Scratch {
     float *qlat, *olat, *top_weight, *row_gate;
     int32_t *top_expert;
     int64_t moe_bytes;
+    // parallel blocks
+    float *x0, *of32;
+    char *h1, *h2, *y2, *yf, *conv;
     int64_t total;
 };
 
@@ -173,6 +215,13 @@ Scratch carve(const atoma_hybrid_model &m, int64_t T, int64_t S, void *base) {
     s.side_g = take(T * w.side * es);
     s.moe = take(w.moe);
     s.moe_bytes = w.moe;
+    s.x0 = reinterpret_cast<float *>(take(w.keep_embedding ? T * m.width * 4 : 0));
+    s.of32 = reinterpret_cast<float *>(take(T * w.of32 * 4));
+    s.h1 = take(w.parallel ? T * m.width * es : 0);
+    s.h2 = take(w.parallel ? T * m.width * es : 0);
+    s.y2 = take(w.parallel ? T * m.width * es : 0);
+    s.yf = take(w.parallel ? T * m.width * es : 0);
+    s.conv = take(T * w.conv * es);
     s.total = off;
     return s;
 }
@@ -480,6 +529,256 @@ bool lanes_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, const
     return hyb_lanes_update_norm(f, stream);
 }
 
+// One layer of a parallel design: h = norm1(x) (in s.h on entry); the mixer reads h + taps1(h), the feed-forward h + taps2(h);
+// x += mixer + feed-forward, then whatever precedes the next layer (`next`, may be NULL), then its norm1 into s.h.
+bool parallel_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, const atoma_hybrid_layer &l, const Scratch &s,
+                    const atoma_hybrid_layer *next, float *trace, cudaStream_t stream) {
+    const uint32_t dt = m.dtype;
+    const int64_t es = dt == ATOMA_DTYPE_F32 ? 4 : 2;
+    const int64_t T = b.num_tokens, W = m.width;
+    if (!l.layer_state && (l.taps > 1 || l.mixer == ATOMA_MIXER_GLA || l.mixer == ATOMA_MIXER_PAIR)) {
+        set_status(kErrInvalidArg, "atoma_hybrid_step: a parallel layer with carried inputs or a recurrence has no state");
+        return false;
+    }
+    // ---- the two sublayers' inputs ----
+    const char *hm = s.h, *hf = s.h;
+    const int64_t hist = l.taps > 1 ? (l.taps - 1) * W : 0;   // floats of the layer's state row that the input history takes
+    if (l.taps > 1) {
+        atoma_tap_filter_args f{};
+        f.in = s.h;
+        f.ld_in = W;
+        f.w1 = l.tap_w1;
+        f.w2 = l.has_mlp ? l.tap_w2 : nullptr;
+        f.out1 = s.h1;
+        f.out2 = l.has_mlp ? s.h2 : nullptr;
+        f.ld_out = W;
+        f.history = l.layer_state;
+        f.history_stride = l.layer_state_stride;
+        f.state_slots = b.state_slots;
+        f.token_seq = b.token_seq;
+        f.query_start = b.query_start;
+        f.context_lens = b.context_lens;
+        f.T = T;
+        f.B = b.num_seqs;
+        f.channels = W;
+        f.taps = l.taps;
+        f.residual = 1;
+        f.act = 0;
+        f.dtype = dt;
+        if (!hyb_tap_filter(f, stream)) return false;
+        hm = s.h1;
+        hf = s.h2;
+    }
+    // ---- feed-forward ----
+    if (l.has_mlp) {
+        if (!hyb_gate_up_act(hf, l.w_gate_up, s.proj, s.act, T, l.ff, W, l.act, dt, stream)) return false;
+        if (!hyb_linear(s.act, l.w_down, s.yf, T, W, l.ff, dt, stream)) return false;
+    }
+    // ---- mixer ----
+    atoma_parallel_residual_args r{};
+    r.mix_scale = 1.f;
+    const int64_t P = l.proj_cols;
+    if (!hyb_linear(hm, l.w_qkv, s.proj, T, P, W, dt, stream)) return false;
+    if (l.mixer == ATOMA_MIXER_GLA) {
+        const int64_t H = l.heads, D = l.dim, V = l.vdim;
+        // decay pre-activation through its low-rank pair: the first product's columns are dense in s.cq
+        if (!hyb_linear(hm, static_cast<const char *>(l.w_qkv) + l.a_off * W * es, s.cq, T, l.a_rank, W, dt, stream)) return false;
+        if (!hyb_linear(s.cq, l.w_a2, s.q, T, H * D, l.a_rank, dt, stream)) return false;
+        atoma_state_scan_args a{};
+        a.kind = 0;
+        a.q = s.proj + l.q_off * es;
+        a.k = s.proj + l.k_off * es;
+        a.v = s.proj + l.v_off * es;
+        a.z = s.q;
+        a.ld_q = a.ld_k = a.ld_v = P;
+        a.ld_z = H * D;
+        a.z_bias = l.a2_bias;
+        a.tau = l.tau;
+        a.q_scale = l.scale;
+        a.state = l.layer_state + hist;
+        a.state_stride = l.layer_state_stride;
+        a.state_slots = b.state_slots;
+        a.query_start = b.query_start;
+        a.context_lens = b.context_lens;
+        a.out = s.of32;
+        a.T = T;
+        a.B = b.num_seqs;
+        a.H = H;
+        a.G = H;
+        a.dim = D;
+        a.vdim = V;
+        a.dtype = dt;
+        if (!hyb_state_scan(a, stream)) return false;
+        if (!hyb_headnorm_gate(s.of32, l.head_norm, s.proj + l.g_off * es, P, s.act, T, H, V, m.eps, dt, stream)) return false;
+        if (!hyb_linear(s.act, l.w_o, s.y, T, W, H * V, dt, stream)) return false;
+        r.y_a = s.y;
+    } else if (l.mixer == ATOMA_MIXER_LATENT_ATTENTION) {
+        const int64_t H = l.heads, row = l.kv_rank + l.rot_dim;
+        if (!hyb_latent_norm_rope_cache(s.proj, P, l.dq_norm, l.dkv_norm, l.qk_freq, l.rot_pairs, l.rot_interleaved, b.positions, b.slot_mapping,
+                                        s.cq, l.latent_cache, T, l.q_rank, l.kv_rank, l.rot_dim, m.eps, dt, stream))
+            return false;
+        if (!hyb_linear(s.cq, l.w_uq, s.q, T, H * (l.dim + l.rot_dim), l.q_rank, dt, stream)) return false;
+        if (!hyb_latent_query_absorb_rope(s.q, l.w_uk, l.qk_freq, l.rot_pairs, l.rot_interleaved, b.positions, s.qlat, T, H, l.dim, l.rot_dim,
+                                          l.kv_rank, dt, stream))
+            return false;
+        atoma_latent_attn_args a{};
+        a.q_lat = s.qlat;
+        a.latent_cache = l.latent_cache;
+        a.out = s.olat;
+        a.positions = b.positions;
+        a.token_seq = b.token_seq;
+        a.query_start = b.query_start;
+        a.block_tables = b.block_tables;
+        a.sink = l.sink;
+        a.T = T;
+        a.B = b.num_seqs;
+        a.max_blocks = b.max_blocks;
+        a.H = H;
+        a.R = row;
+        a.block_size = m.block_size;
+        a.window = l.window;
+        a.scale = l.scale;
+        a.dtype = dt;
+        a.max_query_len = b.max_query_len;
+        a.max_seq_len = b.max_seq_len;
+        if (!hyb_latent_attention(a, stream)) return false;
+        if (!hyb_latent_expand_values(s.olat, l.w_uv, s.act, T, H, l.vdim, l.kv_rank, row, dt, stream)) return false;
+        if (!hyb_linear(s.act, l.w_o, s.y, T, W, H * l.vdim, dt, stream)) return false;
+        r.y_a = s.y;
+    } else if (l.mixer == ATOMA_MIXER_PAIR) {
+        // left: sigmoid attention with rotary positions on queries, keys and values
+        atoma_qkv_rope_args q{};
+        q.proj = s.proj;
+        q.ld = P;
+        q.q_off = l.q_off;
+        q.k_off = l.k_off;
+        q.v_off = l.v_off;
+        q.q_weight = l.q_norm;
+        q.k_weight = l.k_norm;
+        q.qk_freq = l.qk_freq;
+        q.v_freq = l.v_freq;
+        q.rot_pairs = l.rot_pairs;
+        q.v_pairs = l.v_pairs;
+        q.interleaved = l.rot_interleaved;
+        q.positions = b.positions;
+        q.slot_mapping = b.slot_mapping;
+        q.q_out = s.q;
+        q.k_cache = l.k_cache;
+        q.v_cache = l.v_cache;
+        q.T = T;
+        q.H = l.heads;
+        q.G = l.kv_heads;
+        q.dim = l.dim;
+        q.vdim = l.vdim;
+        q.eps = m.eps;
+        q.dtype = dt;
+        if (!hyb_qkv_headnorm_rope_cache(q, stream)) return false;
+        atoma_sigmoid_attn_args a{};
+        a.q = s.q;
+        a.k_cache = l.k_cache;
+        a.v_cache = l.v_cache;
+        a.out = s.act;
+        a.positions = b.positions;
+        a.token_seq = b.token_seq;
+        a.query_start = b.query_start;
+        a.max_seq_len = b.max_seq_len;
+        a.block_tables = b.block_tables;
+        a.slopes = l.slopes;
+        a.head_bias = l.head_bias;
+        a.talk = nullptr;
+        a.T = T;
+        a.B = b.num_seqs;
+        a.max_blocks = b.max_blocks;
+        a.H = l.heads;
+        a.G = l.kv_heads;
+        a.dim = l.dim;
+        a.vdim = l.vdim;
+        a.block_size = m.block_size;
+        a.scale = l.scale;
+        a.softcap = 0.f;
+        a.dtype = dt;
+        a.max_query_len = b.max_query_len;
+        if (!hyb_attention(a, stream)) return false;
+        if (l.v_freq && !hyb_rotate_heads(s.act, b.positions, l.v_freq, T, l.heads, l.vdim, l.v_pairs, l.rot_interleaved, -1.f, dt, stream))
+            return false;
+        if (!hyb_linear(s.act, l.w_o, s.y, T, W, l.heads * l.vdim, dt, stream)) return false;
+        // right: gated delta rule behind short filters
+        const int64_t RH = l.r_heads, RG = l.r_kv_heads, RD = l.r_dim, RV = l.r_vdim;
+        const int64_t C = 2 * RG * RD + RH * RV;
+        atoma_tap_filter_args f{};
+        f.in = s.proj + l.rq_off * es;     // q, k, v columns are neighbours in the stacked projection
+        f.ld_in = P;
+        f.w1 = l.r_tap_w;
+        f.out1 = s.conv;
+        f.ld_out = C;
+        f.history = l.layer_state + hist;
+        f.history_stride = l.layer_state_stride;
+        f.state_slots = b.state_slots;
+        f.token_seq = b.token_seq;
+        f.query_start = b.query_start;
+        f.context_lens = b.context_lens;
+        f.T = T;
+        f.B = b.num_seqs;
+        f.channels = C;
+        f.taps = l.r_taps;
+        f.residual = 0;
+        f.act = 1;
+        f.dtype = dt;
+        if (!hyb_tap_filter(f, stream)) return false;
+        atoma_state_scan_args d{};
+        d.kind = 1;
+        d.q = s.conv;
+        d.k = s.conv + RG * RD * es;
+        d.v = s.conv + 2 * RG * RD * es;
+        d.ld_q = d.ld_k = d.ld_v = C;
+        d.b_pre = s.proj + l.rb_off * es;
+        d.a_pre = s.proj + l.ra_off * es;
+        d.ld_b = d.ld_a = P;
+        d.a_log = l.r_a_log;
+        d.dt_bias = l.r_dt_bias;
+        d.q_scale = 1.0f / sqrtf(static_cast<float>(RD));
+        d.unit_eps = 1e-6f;
+        d.state = l.layer_state + hist + (l.r_taps > 1 ? (l.r_taps - 1) * C : 0);
+        d.state_stride = l.layer_state_stride;
+        d.state_slots = b.state_slots;
+        d.query_start = b.query_start;
+        d.context_lens = b.context_lens;
+        d.out = s.of32;
+        d.T = T;
+        d.B = b.num_seqs;
+        d.H = RH;
+        d.G = RG;
+        d.dim = RD;
+        d.vdim = RV;
+        d.dtype = dt;
+        if (!hyb_state_scan(d, stream)) return false;
+        if (!hyb_headnorm_gate(s.of32, l.r_head_norm, s.proj + l.rg_off * es, P, s.act, T, RH, RV, m.eps, dt, stream)) return false;
+        if (!hyb_linear(s.act, l.r_w_o, s.y2, T, W, RH * RV, dt, stream)) return false;
+        r.y_a = s.y;
+        r.y_b = s.y2;
+        r.norm_a = l.out_norm_a;
+        r.norm_b = l.out_norm_b;
+        r.mix_scale = 0.5f;
+    } else {
+        set_status(kErrUnsupported, "atoma_hybrid_step: parallel layers take gated linear attention, latent attention or the pair of mixers, got %d",
+                   l.mixer);
+        return false;
+    }
+    r.y_ff = l.has_mlp ? s.yf : nullptr;
+    r.x = s.x;
+    r.trace = trace;
+    r.add_rows = next && next->add_embedding ? s.x0 : nullptr;
+    r.add_vec = next ? next->add_vec : nullptr;
+    r.w_next = next ? next->norm1 : nullptr;
+    r.h = s.h;
+    r.T = T;
+    r.width = W;
+    r.eps = m.eps;
+    r.weight_offset = m.norm_offset;
+    r.dtype = dt;
+    return hyb_parallel_residual_norm(r, stream);
+}
+
 }  // namespace
 }  // namespace atoma
 
@@ -497,6 +796,10 @@ extern "C" int64_t atoma_hybrid_abi_sizeof(int which) {
         case 7: return sizeof(atoma_latent_expanded_args);
         case 8: return sizeof(atoma_lanes_update_args);
         case 9: return sizeof(atoma_softmax_attn_args);
+        case 10: return sizeof(atoma_parallel_residual_args);
+        case 11: return sizeof(atoma_tap_filter_args);
+        case 12: return sizeof(atoma_state_scan_args);
+        case 13: return sizeof(atoma_qkv_rope_args);
         default: return -1;
     }
 }
@@ -518,7 +821,7 @@ extern "C" void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_h
     const int64_t T = b.num_tokens, B = b.num_seqs, S = b.num_selected;
     if (T <= 0 || B <= 0) return;
     if (!b.tokens || !b.positions || !b.slot_mapping || !b.token_seq || !b.query_start || !b.context_lens || !b.block_tables ||
-        !b.state_slots || !b.scratch || (S > 0 && (!b.selected || !b.logits)) || !m.embed || (!m.inv_freq && !m.pos_table && m.block_style != ATOMA_BLOCK_LANES) || !m.final_norm ||
+        !b.state_slots || !b.scratch || (S > 0 && (!b.selected || !b.logits)) || !m.embed || (!m.inv_freq && !m.pos_table && m.block_style != ATOMA_BLOCK_LANES && m.block_style != ATOMA_BLOCK_PARALLEL) || !m.final_norm ||
         !m.head || m.width <= 0 || m.vocab <= 0 || m.num_layers <= 0) {
         set_status(kErrInvalidArg, "atoma_hybrid_step: a required tensor is NULL");
         return;
@@ -537,6 +840,35 @@ extern "C" void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_h
     const int64_t W = m.width;
     const float off = m.norm_offset;
     const int64_t groups = m.norm_groups > 0 ? m.norm_groups : 1;
+    if (m.block_style == ATOMA_BLOCK_PARALLEL) {
+        // the embedding rows (kept when a later pass adds them again), what precedes the first layer, its input norm
+        const atoma_hybrid_layer &first = m.layers[0];
+        if (!hyb_embed_scaled_lanes(b.tokens, m.embed, 1.f, s.x, T, 1, W, m.vocab, dt, stream)) return;
+        if (s.x0) cudaMemcpyAsync(s.x0, s.x, static_cast<size_t>(T) * W * 4, cudaMemcpyDeviceToDevice, stream);
+        atoma_parallel_residual_args r{};
+        r.x = s.x;
+        r.add_rows = first.add_embedding ? s.x0 : nullptr;
+        r.add_vec = first.add_vec;
+        r.w_next = first.norm1;
+        r.h = s.h;
+        r.T = T;
+        r.width = W;
+        r.eps = m.eps;
+        r.weight_offset = off;
+        r.dtype = dt;
+        if (!hyb_parallel_residual_norm(r, stream)) return;
+        for (int64_t i = 0; i < m.num_layers; ++i) {
+            if (!parallel_layer(m, b, m.layers[i], s, i + 1 < m.num_layers ? &m.layers[i + 1] : nullptr,
+                                b.residual_trace ? b.residual_trace + i * T * W : nullptr, stream))
+                return;
+        }
+        if (S > 0) {
+            if (!hyb_group_rmsnorm_rows(s.x, b.selected, m.final_norm, off, 1, s.hs, S, W, m.eps, dt, stream)) return;
+            if (!hyb_linear(s.hs, m.head, s.lg, S, m.vocab, W, dt, stream)) return;
+            if (!hyb_scale_greedy(s.lg, b.logits, b.next_tokens, S, m.vocab, m.logit_scale, m.logit_softcap, dt, stream)) return;
+        }
+        return;
+    }
     if (m.block_style == ATOMA_BLOCK_LANES) {
         // scaled embedding into every lane; per layer the lanes are read, normed, run through the sublayer and written back
         const int64_t lanes = m.lanes;

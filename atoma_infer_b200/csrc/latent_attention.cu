@@ -586,8 +586,11 @@ bool hyb_latent_norm_cache(const void *proj, int64_t ld, const float *q_w, const
 #undef CALL
 }
 
-bool hyb_head_project(const void *in, const void *w, void *out, int64_t T, int64_t H, int64_t n, int64_t R, int32_t absorb, uint32_t dtype,
-                      cudaStream_t stream) {
+// Per-head projection with explicit strides: head h of `in` starts in_hs elements into a row of ld_in, head h of `out`
+// out_hs elements into a row of ld_out (so heads that carry more than the projected part, or an output row that keeps
+// room for more, need no copies).  w [H n, R] as in atoma_head_project.
+bool hyb_head_project_ld(const void *in, int64_t ld_in, int64_t in_hs, const void *w, void *out, int64_t ld_out, int64_t out_hs, int64_t T,
+                         int64_t H, int64_t n, int64_t R, int32_t absorb, uint32_t dtype, cudaStream_t stream) {
     if (T <= 0) return true;
     if (!hybrid::known_dtype(dtype, "atoma_head_project")) return false;
     if (!in || !w || !out || H <= 0 || n <= 0 || R <= 0) {
@@ -603,12 +606,13 @@ bool hyb_head_project(const void *in, const void *w, void *out, int64_t T, int64
         p.o = out;
         p.b_zs = n * R;
         p.M = M;
+        p.lda = ld_in, p.a_zs = in_hs, p.ldo = ld_out, p.o_zs = out_hs;
         if (absorb) {
-            p.lda = H * n, p.a_zs = n, p.b_ks = R, p.b_ns = 1, p.ldo = H * R, p.o_zs = R, p.N = static_cast<int>(R), p.K = static_cast<int>(n);
+            p.b_ks = R, p.b_ns = 1, p.N = static_cast<int>(R), p.K = static_cast<int>(n);
             const dim3 grid(static_cast<unsigned>((R + 63) / 64), static_cast<unsigned>((T + 63) / 64), static_cast<unsigned>(H));
             e = launch_ex(tc::gemm_kernel<__nv_bfloat16, float, false>, grid, dim3(128), 0, stream, p);
         } else {
-            p.lda = H * R, p.a_zs = R, p.b_ks = 1, p.b_ns = R, p.ldo = H * n, p.o_zs = n, p.N = static_cast<int>(n), p.K = static_cast<int>(R);
+            p.b_ks = 1, p.b_ns = R, p.N = static_cast<int>(n), p.K = static_cast<int>(R);
             const dim3 grid(static_cast<unsigned>((n + 63) / 64), static_cast<unsigned>((T + 63) / 64), static_cast<unsigned>(H));
             e = launch_ex(tc::gemm_kernel<float, __nv_bfloat16, false>, grid, dim3(128), 0, stream, p);
         }
@@ -616,20 +620,26 @@ bool hyb_head_project(const void *in, const void *w, void *out, int64_t T, int64
     }
     if (absorb) {
         const dim3 grid(static_cast<unsigned>((R + 63) / 64), static_cast<unsigned>((T + 63) / 64), static_cast<unsigned>(H));
-#define CALL(TT) launch_ex(head_project_kernel<TT, TT, float>, grid, dim3(256), 0, stream, static_cast<const TT *>(in), H * n, n, \
-                           static_cast<const TT *>(w), n * R, R, static_cast<int64_t>(1), static_cast<float *>(out), H * R, R, M, \
+#define CALL(TT) launch_ex(head_project_kernel<TT, TT, float>, grid, dim3(256), 0, stream, static_cast<const TT *>(in), ld_in, in_hs, \
+                           static_cast<const TT *>(w), n * R, R, static_cast<int64_t>(1), static_cast<float *>(out), ld_out, out_hs, M, \
                            static_cast<int>(R), static_cast<int>(n))
         e = HYB_DISPATCH(dtype, CALL);
 #undef CALL
     } else {
         const dim3 grid(static_cast<unsigned>((n + 63) / 64), static_cast<unsigned>((T + 63) / 64), static_cast<unsigned>(H));
-#define CALL(TT) launch_ex(head_project_kernel<float, TT, TT>, grid, dim3(256), 0, stream, static_cast<const float *>(in), H * R, R, \
-                           static_cast<const TT *>(w), n * R, static_cast<int64_t>(1), R, static_cast<TT *>(out), H * n, n, M, \
+#define CALL(TT) launch_ex(head_project_kernel<float, TT, TT>, grid, dim3(256), 0, stream, static_cast<const float *>(in), ld_in, in_hs, \
+                           static_cast<const TT *>(w), n * R, static_cast<int64_t>(1), R, static_cast<TT *>(out), ld_out, out_hs, M, \
                            static_cast<int>(n), static_cast<int>(R))
         e = HYB_DISPATCH(dtype, CALL);
 #undef CALL
     }
     return hybrid::launched(e, "head_project_kernel");
+}
+
+bool hyb_head_project(const void *in, const void *w, void *out, int64_t T, int64_t H, int64_t n, int64_t R, int32_t absorb, uint32_t dtype,
+                      cudaStream_t stream) {
+    if (absorb) return hyb_head_project_ld(in, H * n, n, w, out, H * R, R, T, H, n, R, 1, dtype, stream);
+    return hyb_head_project_ld(in, H * R, R, w, out, H * n, n, T, H, n, R, 0, dtype, stream);
 }
 
 // The tensor-core kernel takes bfloat16 caches whose latent size is a multiple of 64 up to 256 (four warps) or a multiple of

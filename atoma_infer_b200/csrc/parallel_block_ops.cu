@@ -1,0 +1,728 @@
+// Operators of PARALLEL decoder blocks and their mixers — include/atoma_hybrid.h.
+//
+// A parallel block norms the residual stream once; the mixer and the feed-forward both read that row, each through a
+// causal tap filter over time, and both results join the stream in one update (fused here with whatever precedes the next
+// layer and with its input norm).  The mixers that need more than attention kernels:
+//   - tap filters whose inputs before a portion come from a per-sequence history (the portion's last inputs replace it),
+//   - matrix-state recurrences (gated linear attention, gated delta rule): every head keeps S [dim, vdim] in float32; the
+//     columns of S are independent in both recurrences, so a CTA owns 32 columns of one head of one sequence, the rows
+//     of a column are spread over `parts` threads (registers), and the tokens are visited strictly in order,
+//   - rotary positions on queries, keys and values with the cache write, the turn-back of a head's sum, and the
+//     latent-attention variants that keep one rotated key part beside the latent.
+// Statistics, angles, decays, gates of the recurrences and the state are float32 whatever the activation format; every
+// result is reduced in an order that depends on the token alone, never on the batch around it.
+#include "common.cuh"
+#include "hybrid_common.cuh"
+
+#include "atoma_hybrid.h"
+
+#include <algorithm>
+
+namespace atoma {
+
+bool hyb_head_project_ld(const void *, int64_t, int64_t, const void *, void *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int32_t,
+                         uint32_t, cudaStream_t);   // latent_attention.cu
+
+namespace {
+
+using namespace hybrid;
+
+constexpr int kMaxTaps = 16;
+constexpr int kScanCols = 32;     // columns of the state per CTA
+constexpr int kScanChunk = 8;     // tokens staged in shared memory at a time
+
+// ---------------------------------------------------------------------------------------------
+// residual update of a parallel block + what precedes the next layer + its input norm
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) parallel_residual_norm_kernel(const atoma_parallel_residual_args a) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    const int W = static_cast<int>(a.width);
+    const T *ya = a.y_a ? static_cast<const T *>(a.y_a) + t * W : nullptr;
+    const T *yb = a.y_b ? static_cast<const T *>(a.y_b) + t * W : nullptr;
+    const T *yf = a.y_ff ? static_cast<const T *>(a.y_ff) + t * W : nullptr;
+    float inv_a = 1.f, inv_b = 1.f;
+    if (ya && a.norm_a) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            const float v = to_f(ya[c]);
+            ss = fmaf(v, v, ss);
+        }
+        inv_a = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(W) + a.eps);
+    }
+    if (yb && a.norm_b) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            const float v = to_f(yb[c]);
+            ss = fmaf(v, v, ss);
+        }
+        inv_b = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(W) + a.eps);
+    }
+    float *x = a.x + t * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float m = 0.f;
+        if (ya) m += a.norm_a ? to_f(ya[c]) * inv_a * a.norm_a[c] : to_f(ya[c]);
+        if (yb) m += a.norm_b ? to_f(yb[c]) * inv_b * a.norm_b[c] : to_f(yb[c]);
+        float v = x[c] + a.mix_scale * m;
+        if (yf) v += to_f(yf[c]);
+        if (a.trace) a.trace[t * W + c] = v;
+        if (a.add_rows) v += a.add_rows[t * W + c];
+        if (a.add_vec) v += a.add_vec[c];
+        x[c] = v;
+        row[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!a.w_next) return;
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(W) + a.eps);
+    T *h = static_cast<T *>(a.h) + t * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) h[c] = from_f<T>(row[c] * inv * (a.weight_offset + a.w_next[c]));
+}
+
+// ---------------------------------------------------------------------------------------------
+// tap filters with carried inputs
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) tap_filter_kernel(const atoma_tap_filter_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int C = static_cast<int>(a.channels), taps = static_cast<int>(a.taps);
+    if (c >= C) return;
+    const int b = a.token_seq[t];
+    const int i = static_cast<int>(t) - a.query_start[b];     // index inside the portion
+    const int ctx = a.context_lens[b];
+    const T *in = static_cast<const T *>(a.in);
+    const float *hist = a.history ? a.history + static_cast<int64_t>(a.state_slots[b]) * a.history_stride : nullptr;
+    const float cur = to_f(in[t * a.ld_in + c]);
+    float f1 = 0.f, f2 = 0.f;
+    for (int j = 0; j + 1 < taps; ++j) {
+        const int back = taps - 1 - j;
+        float v = 0.f;
+        if (i - back >= 0) v = to_f(in[(t - back) * a.ld_in + c]);
+        else if (ctx + i - back >= 0 && hist) v = hist[static_cast<int64_t>(taps - 1 + i - back) * C + c];
+        f1 = fmaf(a.w1[c * taps + j], v, f1);
+        if (a.w2) f2 = fmaf(a.w2[c * taps + j], v, f2);
+    }
+    f1 = fmaf(a.w1[c * taps + taps - 1], cur, f1);
+    if (a.residual) f1 += cur;
+    if (a.act == 1) f1 = silu(f1);
+    static_cast<T *>(a.out1)[t * a.ld_out + c] = from_f<T>(f1);
+    if (a.w2) {
+        f2 = fmaf(a.w2[c * taps + taps - 1], cur, f2);
+        if (a.residual) f2 += cur;
+        if (a.act == 1) f2 = silu(f2);
+        static_cast<T *>(a.out2)[t * a.ld_out + c] = from_f<T>(f2);
+    }
+}
+
+// history[k] <- the sequence's input at position (context + n) - (taps - 1) + k, from the portion or from the old history
+template <typename T>
+__global__ void __launch_bounds__(256) tap_history_kernel(const atoma_tap_filter_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int C = static_cast<int>(a.channels), keep = static_cast<int>(a.taps) - 1;
+    if (c >= C) return;
+    const int q0 = a.query_start[b], n = a.query_start[b + 1] - q0, ctx = a.context_lens[b];
+    if (n <= 0) return;
+    float *hist = a.history + static_cast<int64_t>(a.state_slots[b]) * a.history_stride;
+    const T *in = static_cast<const T *>(a.in);
+    float old[kMaxTaps];
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k) old[k] = (k < keep && k + n < keep && ctx - keep + k + n >= 0) ? hist[static_cast<int64_t>(k + n) * C + c] : 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k) {
+        if (k >= keep) break;
+        const int rel = n - keep + k;
+        hist[static_cast<int64_t>(k) * C + c] = rel >= 0 ? to_f(in[static_cast<int64_t>(q0 + rel) * a.ld_in + c]) : old[k];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// matrix-state recurrences
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// Sum of one value per part for every column; parts write, one barrier, every thread adds the parts in index order.
+template <int RPT>
+__device__ __forceinline__ float part_sum(float v, float *red, int parts, int part, int col) {
+    if (parts == 1) return v;
+    red[part * kScanCols + col] = v;
+    __syncthreads();
+    float s = 0.f;
+    for (int p = 0; p < parts; ++p) s += red[p * kScanCols + col];
+    return s;
+}
+
+template <typename T, int KIND, int RPT>
+__global__ void __launch_bounds__(1024) state_scan_kernel(const atoma_state_scan_args a, int parts) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int col = threadIdx.x, part = threadIdx.y;
+    const int tid = part * kScanCols + col, nthr = parts * kScanCols;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int D = static_cast<int>(a.dim), V = static_cast<int>(a.vdim), H = static_cast<int>(a.H);
+    const int Dp = parts * RPT;                              // padded rows: what lies beyond dim stays zero
+    const int j = blockIdx.x * kScanCols + col;
+    const int q0 = a.query_start[b], n = a.query_start[b + 1] - q0;
+    if (n <= 0) return;
+    float *q_s = sm;                                         // [chunk][Dp]
+    float *k_s = q_s + kScanChunk * Dp;
+    float *a_s = k_s + kScanChunk * Dp;                      // kind 0: decay per key channel; kind 1: [chunk][2] = beta, decay
+    float *v_s = a_s + (KIND == 0 ? kScanChunk * Dp : kScanChunk * 2);   // [chunk][32]
+    float *red = v_s + kScanChunk * kScanCols;               // [2][parts][32]
+    const int kvh = KIND == 1 ? h / (H / static_cast<int>(a.G)) : h;
+    float *S_g = a.state + static_cast<int64_t>(a.state_slots[b]) * a.state_stride + static_cast<int64_t>(h) * D * V;
+    float S[RPT];
+    const bool fresh = a.context_lens[b] == 0;
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+        const int i = part * RPT + r;
+        S[r] = (!fresh && i < D && j < V) ? S_g[static_cast<int64_t>(i) * V + j] : 0.f;
+    }
+    const T *qp = static_cast<const T *>(a.q), *kp = static_cast<const T *>(a.k), *vp = static_cast<const T *>(a.v);
+    int flip = 0;
+    for (int t0 = 0; t0 < n; t0 += kScanChunk) {
+        const int nt = min(kScanChunk, n - t0);
+        __syncthreads();                                     // the previous chunk has been consumed
+        for (int idx = tid; idx < nt * Dp; idx += nthr) {
+            const int tk = idx / Dp, i = idx % Dp;
+            const int64_t t = q0 + t0 + tk;
+            float qv = 0.f, kv = 0.f, av = 0.f;
+            if (i < D) {
+                qv = to_f(qp[t * a.ld_q + kvh * D + i]);
+                kv = to_f(kp[t * a.ld_k + kvh * D + i]);
+                if (KIND == 0) {
+                    qv *= a.q_scale;
+                    const float z = to_f(static_cast<const T *>(a.z)[t * a.ld_z + h * D + i]) + a.z_bias[h * D + i];
+                    av = expf(log_sigmoid(z) / a.tau);
+                }
+            }
+            q_s[idx] = qv;
+            k_s[idx] = kv;
+            if (KIND == 0) a_s[idx] = av;
+        }
+        for (int idx = tid; idx < nt * kScanCols; idx += nthr) {
+            const int tk = idx / kScanCols, cc = idx % kScanCols;
+            const int jj = blockIdx.x * kScanCols + cc;
+            v_s[idx] = jj < V ? to_f(vp[static_cast<int64_t>(q0 + t0 + tk) * a.ld_v + h * V + jj]) : 0.f;
+        }
+        if (KIND == 1) {
+            __syncthreads();
+            // unit length per head: one warp per staged token, lanes over the channels in a fixed order
+            for (int tk = part; tk < nt; tk += parts) {
+                float sq = 0.f, sk = 0.f;
+                for (int i = col; i < D; i += kScanCols) {
+                    sq = fmaf(q_s[tk * Dp + i], q_s[tk * Dp + i], sq);
+                    sk = fmaf(k_s[tk * Dp + i], k_s[tk * Dp + i], sk);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                    sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                }
+                const float iq = a.q_scale / sqrtf(sq + a.unit_eps), ik = 1.0f / sqrtf(sk + a.unit_eps);
+                for (int i = col; i < D; i += kScanCols) {
+                    q_s[tk * Dp + i] *= iq;
+                    k_s[tk * Dp + i] *= ik;
+                }
+                if (col == 0) {
+                    const int64_t t = q0 + t0 + tk;
+                    const float bp = to_f(static_cast<const T *>(a.b_pre)[t * a.ld_b + h]);
+                    const float ap = to_f(static_cast<const T *>(a.a_pre)[t * a.ld_a + h]) + a.dt_bias[h];
+                    a_s[tk * 2] = sigmoidf_(bp);
+                    a_s[tk * 2 + 1] = expf(-expf(a.a_log[h]) * softplusf_(ap));
+                }
+            }
+        }
+        __syncthreads();
+        for (int tk = 0; tk < nt; ++tk) {
+            const float *qr = q_s + tk * Dp + part * RPT, *kr = k_s + tk * Dp + part * RPT;
+            const float vj = v_s[tk * kScanCols + col];
+            float o;
+            if (KIND == 0) {
+                const float *ar = a_s + tk * Dp + part * RPT;
+                float acc = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPT; ++r) {
+                    S[r] = fmaf(ar[r], S[r], kr[r] * vj);
+                    acc = fmaf(S[r], qr[r], acc);
+                }
+                o = part_sum<RPT>(acc, red + flip * parts * kScanCols, parts, part, col);
+                flip ^= 1;
+            } else {
+                const float beta = a_s[tk * 2], g = a_s[tk * 2 + 1];
+                float acc = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPT; ++r) {
+                    S[r] *= g;
+                    acc = fmaf(S[r], kr[r], acc);
+                }
+                const float read = part_sum<RPT>(acc, red, parts, part, col);
+                const float u = beta * (vj - read);
+                acc = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPT; ++r) {
+                    S[r] = fmaf(kr[r], u, S[r]);
+                    acc = fmaf(S[r], qr[r], acc);
+                }
+                o = part_sum<RPT>(acc, red + parts * kScanCols, parts, part, col);
+            }
+            if (part == 0 && j < V) a.out[static_cast<int64_t>(q0 + t0 + tk) * H * V + h * V + j] = o;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+        const int i = part * RPT + r;
+        if (i < D && j < V) S_g[static_cast<int64_t>(i) * V + j] = S[r];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-head RMS norm of a float32 read-out, times a gate
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) headnorm_gate_kernel(const float *__restrict__ o, const float *__restrict__ weight,
+                                                            const T *__restrict__ gate, int64_t ld_gate, T *__restrict__ out, int H, int V,
+                                                            float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int h = warp; h < H; h += nwarp) {
+        const float *r = o + (t * H + h) * V;
+        float ss = 0.f;
+        for (int c = lane; c < V; c += 32) ss = fmaf(r[c], r[c], ss);
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+        const float inv = 1.0f / sqrtf(ss / static_cast<float>(V) + eps);
+        for (int c = lane; c < V; c += 32) {
+            float v = r[c] * inv * weight[c];
+            if (gate) v *= silu(to_f(gate[t * ld_gate + h * V + c]));
+            out[(t * H + h) * V + c] = from_f<T>(v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// rotary positions
+// ---------------------------------------------------------------------------------------------
+// buf [n] float32 (one warp's): the first 2 pairs entries turned by sign * pos * freq, written to dst as T.
+template <typename T>
+__device__ __forceinline__ void rotate_store(const float *buf, int n, const float *__restrict__ freq, int pairs, int interleaved, float pos,
+                                             float sign, T *__restrict__ dst, int lane) {
+    for (int i = lane; i < pairs; i += 32) {
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + pairs;
+        float sn, cs;
+        sincosf(pos * freq[i], &sn, &cs);
+        sn *= sign;
+        const float u = buf[ia], v = buf[ib];
+        dst[ia] = from_f<T>(u * cs - v * sn);
+        dst[ib] = from_f<T>(v * cs + u * sn);
+    }
+    for (int i = 2 * pairs + lane; i < n; i += 32) dst[i] = from_f<T>(buf[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_headnorm_rope_cache_kernel(const atoma_qkv_rope_args a) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int H = static_cast<int>(a.H), G = static_cast<int>(a.G), D = static_cast<int>(a.dim), V = static_cast<int>(a.vdim);
+    const int wide = max(D, V);
+    float *buf = sm + warp * wide;
+    const T *row = static_cast<const T *>(a.proj) + t * a.ld;
+    const float pos = static_cast<float>(a.positions[t]);
+    const int64_t slot = a.slot_mapping ? a.slot_mapping[t] : -1;
+    for (int u = warp; u < H + 2 * G; u += nwarp) {
+        const bool is_q = u < H, is_k = !is_q && u < H + G;
+        const int hd = is_q ? u : (is_k ? u - H : u - H - G);
+        if (!is_q && slot < 0) continue;
+        const int n = (is_q || is_k) ? D : V;
+        const T *src = row + (is_q ? a.q_off + hd * D : (is_k ? a.k_off + hd * D : a.v_off + hd * V));
+        const float *w = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
+        float ss = 0.f;
+        for (int c = lane; c < n; c += 32) {
+            const float v = to_f(src[c]);
+            buf[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+        if (w) {
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+            const float inv = 1.0f / sqrtf(ss / static_cast<float>(n) + a.eps);
+            for (int c = lane; c < n; c += 32) buf[c] = buf[c] * inv * w[c];
+        }
+        __syncwarp();
+        T *dst = is_q ? static_cast<T *>(a.q_out) + (t * H + hd) * D
+                      : (is_k ? static_cast<T *>(a.k_cache) + (slot * G + hd) * D : static_cast<T *>(a.v_cache) + (slot * G + hd) * V);
+        const bool vpart = !is_q && !is_k;
+        const float *freq = vpart ? a.v_freq : a.qk_freq;
+        const int pairs = freq ? static_cast<int>(vpart ? a.v_pairs : a.rot_pairs) : 0;
+        rotate_store<T>(buf, n, freq, pairs, a.interleaved, pos, 1.f, dst, lane);
+        __syncwarp();
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rotate_heads_kernel(T *__restrict__ x, const int64_t *__restrict__ positions,
+                                                           const float *__restrict__ freq, int H, int n, int pairs, int interleaved,
+                                                           float sign) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    const float pos = static_cast<float>(positions[t]);
+    T *row = x + t * H * n;
+    for (int idx = threadIdx.x; idx < H * pairs; idx += blockDim.x) {
+        const int h = idx / pairs, i = idx % pairs;
+        const int ia = h * n + (interleaved ? 2 * i : i), ib = h * n + (interleaved ? 2 * i + 1 : i + pairs);
+        float sn, cs;
+        sincosf(pos * freq[i], &sn, &cs);
+        sn *= sign;
+        const float u = to_f(row[ia]), v = to_f(row[ib]);
+        row[ia] = from_f<T>(u * cs - v * sn);
+        row[ib] = from_f<T>(v * cs + u * sn);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) latent_norm_rope_cache_kernel(const T *__restrict__ proj, int64_t ld,
+                                                                             const float *__restrict__ q_w, const float *__restrict__ kv_w,
+                                                                             const float *__restrict__ freq, int pairs, int interleaved,
+                                                                             const int64_t *__restrict__ positions,
+                                                                             const int64_t *__restrict__ slots, T *__restrict__ cq_out,
+                                                                             T *__restrict__ cache, int q_rank, int kv_rank, int rot_dim,
+                                                                             float eps) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    const T *r = proj + t * ld;
+    if (q_rank > 0) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < q_rank; c += blockDim.x) {
+            const float v = to_f(r[c]);
+            ss = fmaf(v, v, ss);
+        }
+        const float inv = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(q_rank) + eps);
+        for (int c = threadIdx.x; c < q_rank; c += blockDim.x) cq_out[t * q_rank + c] = from_f<T>(to_f(r[c]) * inv * q_w[c]);
+    }
+    const int64_t slot = slots ? slots[t] : -1;
+    if (slot < 0) return;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+        const float v = to_f(r[q_rank + c]);
+        ss = fmaf(v, v, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(kv_rank) + eps);
+    T *dst = cache + slot * (kv_rank + rot_dim);
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) dst[c] = from_f<T>(to_f(r[q_rank + c]) * inv * kv_w[c]);
+    const T *kr = r + q_rank + kv_rank;
+    const float pos = static_cast<float>(positions[t]);
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + pairs;
+        float sn, cs;
+        sincosf(pos * freq[i], &sn, &cs);
+        const float u = to_f(kr[ia]), v = to_f(kr[ib]);
+        dst[kv_rank + ia] = from_f<T>(u * cs - v * sn);
+        dst[kv_rank + ib] = from_f<T>(v * cs + u * sn);
+    }
+    for (int c = 2 * pairs + threadIdx.x; c < rot_dim; c += blockDim.x) dst[kv_rank + c] = kr[c];
+}
+
+// q_lat[t, h, kv_rank + c] = the rotated part of query head h, float32
+template <typename T>
+__global__ void __launch_bounds__(256) latent_query_rope_kernel(const T *__restrict__ q, const float *__restrict__ freq, int pairs,
+                                                                int interleaved, const int64_t *__restrict__ positions,
+                                                                float *__restrict__ q_lat, int H, int dim, int rot_dim, int kv_rank) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    const float pos = static_cast<float>(positions[t]);
+    const int hs = dim + rot_dim, row = kv_rank + rot_dim;
+    for (int idx = threadIdx.x; idx < H * pairs; idx += blockDim.x) {
+        const int h = idx / pairs, i = idx % pairs;
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + pairs;
+        const T *src = q + (t * H + h) * hs + dim;
+        float sn, cs;
+        sincosf(pos * freq[i], &sn, &cs);
+        const float u = to_f(src[ia]), v = to_f(src[ib]);
+        float *dst = q_lat + (t * H + h) * row + kv_rank;
+        dst[ia] = u * cs - v * sn;
+        dst[ib] = v * cs + u * sn;
+    }
+    const int rest = rot_dim - 2 * pairs;
+    for (int idx = threadIdx.x; idx < H * rest; idx += blockDim.x) {
+        const int h = idx / rest, c = 2 * pairs + idx % rest;
+        q_lat[(t * H + h) * row + kv_rank + c] = to_f(q[(t * H + h) * hs + dim + c]);
+    }
+}
+
+}  // namespace
+
+#define HYB_DISPATCH(dtype, CALL) ((dtype) == ATOMA_DTYPE_BF16 ? CALL(__nv_bfloat16) : CALL(float))
+
+bool hyb_parallel_residual_norm(const atoma_parallel_residual_args &a, cudaStream_t stream) {
+    if (a.T <= 0) return true;
+    if (!hybrid::known_dtype(a.dtype, "atoma_parallel_residual_norm")) return false;
+    if (!a.x || a.width <= 0 || (a.w_next && !a.h) || (a.norm_a && !a.y_a) || (a.norm_b && !a.y_b)) {
+        set_status(kErrInvalidArg, "atoma_parallel_residual_norm: null argument");
+        return false;
+    }
+    const size_t smem = static_cast<size_t>(a.width) * 4;
+    if (smem > 200 * 1024) {
+        set_status(kErrUnsupported, "atoma_parallel_residual_norm: a width of %lld exceeds shared memory", static_cast<long long>(a.width));
+        return false;
+    }
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(parallel_residual_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(parallel_residual_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    }
+#define CALL(TT) launch_ex(parallel_residual_norm_kernel<TT>, dim3(static_cast<unsigned>(a.T)), dim3(kRowThreads), smem, stream, a)
+    return hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "parallel_residual_norm_kernel");
+#undef CALL
+}
+
+bool hyb_tap_filter(const atoma_tap_filter_args &a, cudaStream_t stream) {
+    if (a.T <= 0 || a.channels <= 0) return true;
+    if (!hybrid::known_dtype(a.dtype, "atoma_tap_filter")) return false;
+    if (!a.in || !a.w1 || !a.out1 || (a.w2 && !a.out2) || a.taps < 1 || a.taps > kMaxTaps || a.ld_in < a.channels || a.ld_out < a.channels ||
+        !a.token_seq || !a.query_start || !a.context_lens || a.B <= 0 ||
+        (a.taps > 1 && (!a.history || !a.state_slots || a.history_stride < (a.taps - 1) * a.channels))) {
+        set_status(kErrInvalidArg, "atoma_tap_filter: null argument, more than %d taps, or a history row shorter than (taps - 1) channels", kMaxTaps);
+        return false;
+    }
+    const unsigned cb = static_cast<unsigned>((a.channels + 255) / 256);
+#define CALL(TT) launch_ex(tap_filter_kernel<TT>, dim3(cb, static_cast<unsigned>(a.T)), dim3(256), 0, stream, a)
+    if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "tap_filter_kernel")) return false;
+#undef CALL
+    if (a.taps == 1) return true;
+#define CALL(TT) launch_ex(tap_history_kernel<TT>, dim3(cb, static_cast<unsigned>(a.B)), dim3(256), 0, stream, a)
+    return hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "tap_history_kernel");
+#undef CALL
+}
+
+bool hyb_state_scan(const atoma_state_scan_args &a, cudaStream_t stream) {
+    if (a.T <= 0 || a.B <= 0) return true;
+    if (!hybrid::known_dtype(a.dtype, "atoma_state_scan")) return false;
+    const bool gla = a.kind == 0, delta = a.kind == 1;
+    if ((!gla && !delta) || !a.q || !a.k || !a.v || !a.state || !a.state_slots || !a.query_start || !a.context_lens || !a.out || a.H <= 0 ||
+        a.dim <= 0 || a.vdim <= 0 || a.state_stride < a.H * a.dim * a.vdim || (gla && (!a.z || !a.z_bias || !(a.tau > 0.f))) ||
+        (delta && (!a.b_pre || !a.a_pre || !a.a_log || !a.dt_bias || a.G <= 0 || a.H % a.G))) {
+        set_status(kErrInvalidArg, "atoma_state_scan: null argument, unknown kind %d, or a state row shorter than heads * dim * vdim", a.kind);
+        return false;
+    }
+    const int rpt = a.dim <= 64 ? 16 : 32;
+    const int parts = static_cast<int>((a.dim + rpt - 1) / rpt);
+    if (parts > 32) {
+        set_status(kErrUnsupported, "atoma_state_scan: a key size of %lld exceeds 1024", static_cast<long long>(a.dim));
+        return false;
+    }
+    const int Dp = parts * rpt;
+    const size_t smem = static_cast<size_t>(2 * kScanChunk * Dp + (gla ? kScanChunk * Dp : kScanChunk * 2) + kScanChunk * kScanCols +
+                                            2 * parts * kScanCols) * 4;
+    const dim3 grid(static_cast<unsigned>((a.vdim + kScanCols - 1) / kScanCols), static_cast<unsigned>(a.H), static_cast<unsigned>(a.B));
+    const dim3 block(kScanCols, static_cast<unsigned>(parts));
+    cudaError_t e;
+#define SCAN(TT, KIND, RPT)                                                                                                  \
+    do {                                                                                                                      \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(state_scan_kernel<TT, KIND, RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+        e = launch_ex(state_scan_kernel<TT, KIND, RPT>, grid, block, smem, stream, a, parts);                                 \
+    } while (0)
+#define SCAN_T(TT)                                      \
+    do {                                                \
+        if (gla && rpt == 16) SCAN(TT, 0, 16);          \
+        else if (gla) SCAN(TT, 0, 32);                  \
+        else if (rpt == 16) SCAN(TT, 1, 16);            \
+        else SCAN(TT, 1, 32);                           \
+    } while (0)
+    if (a.dtype == ATOMA_DTYPE_BF16) SCAN_T(__nv_bfloat16);
+    else SCAN_T(float);
+#undef SCAN_T
+#undef SCAN
+    return hybrid::launched(e, "state_scan_kernel");
+}
+
+bool hyb_headnorm_gate(const float *o, const float *weight, const void *gate, int64_t ld_gate, void *out, int64_t T, int64_t H, int64_t vdim,
+                       float eps, uint32_t dtype, cudaStream_t stream) {
+    if (T <= 0) return true;
+    if (!hybrid::known_dtype(dtype, "atoma_headnorm_gate")) return false;
+    if (!o || !weight || !out || H <= 0 || vdim <= 0 || (gate && ld_gate < H * vdim)) {
+        set_status(kErrInvalidArg, "atoma_headnorm_gate: null argument or a gate row shorter than heads * vdim");
+        return false;
+    }
+    const unsigned threads = static_cast<unsigned>(std::min<int64_t>(8, H) * 32);
+#define CALL(TT) launch_ex(headnorm_gate_kernel<TT>, dim3(static_cast<unsigned>(T)), dim3(threads), 0, stream, o, weight, \
+                           static_cast<const TT *>(gate), ld_gate, static_cast<TT *>(out), static_cast<int>(H), static_cast<int>(vdim), eps)
+    return hybrid::launched(HYB_DISPATCH(dtype, CALL), "headnorm_gate_kernel");
+#undef CALL
+}
+
+bool hyb_qkv_headnorm_rope_cache(const atoma_qkv_rope_args &a, cudaStream_t stream) {
+    if (a.T <= 0) return true;
+    if (!hybrid::known_dtype(a.dtype, "atoma_qkv_headnorm_rope_cache")) return false;
+    if (!a.proj || !a.q_out || !a.positions || a.H <= 0 || a.G <= 0 || a.H % a.G || a.dim <= 0 || a.vdim <= 0 ||
+        (a.slot_mapping && (!a.k_cache || !a.v_cache)) || a.q_off < 0 || a.k_off < 0 || a.v_off < 0 || a.q_off + a.H * a.dim > a.ld ||
+        a.k_off + a.G * a.dim > a.ld || a.v_off + a.G * a.vdim > a.ld || a.rot_pairs < 0 || 2 * a.rot_pairs > a.dim || a.v_pairs < 0 ||
+        2 * a.v_pairs > a.vdim || (a.rot_pairs > 0 && !a.qk_freq)) {
+        set_status(kErrInvalidArg, "atoma_qkv_headnorm_rope_cache: null argument, columns outside the row, or more rotated entries than a head has");
+        return false;
+    }
+    const unsigned warps = static_cast<unsigned>(std::min<int64_t>(8, a.H + 2 * a.G));
+    const size_t smem = static_cast<size_t>(warps) * std::max(a.dim, a.vdim) * 4;
+    if (smem > 48 * 1024) {
+        set_status(kErrUnsupported, "atoma_qkv_headnorm_rope_cache: heads of %lld entries", static_cast<long long>(std::max(a.dim, a.vdim)));
+        return false;
+    }
+#define CALL(TT) launch_ex(qkv_headnorm_rope_cache_kernel<TT>, dim3(static_cast<unsigned>(a.T)), dim3(warps * 32), smem, stream, a)
+    return hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "qkv_headnorm_rope_cache_kernel");
+#undef CALL
+}
+
+bool hyb_rotate_heads(void *x, const int64_t *positions, const float *freq, int64_t T, int64_t H, int64_t n, int64_t pairs, int32_t interleaved,
+                      float sign, uint32_t dtype, cudaStream_t stream) {
+    if (T <= 0 || pairs <= 0) return true;
+    if (!hybrid::known_dtype(dtype, "atoma_rotate_heads")) return false;
+    if (!x || !positions || !freq || H <= 0 || 2 * pairs > n) {
+        set_status(kErrInvalidArg, "atoma_rotate_heads: null argument or more rotated entries than a head has");
+        return false;
+    }
+#define CALL(TT) launch_ex(rotate_heads_kernel<TT>, dim3(static_cast<unsigned>(T)), dim3(256), 0, stream, static_cast<TT *>(x), positions, freq, \
+                           static_cast<int>(H), static_cast<int>(n), static_cast<int>(pairs), interleaved, sign)
+    return hybrid::launched(HYB_DISPATCH(dtype, CALL), "rotate_heads_kernel");
+#undef CALL
+}
+
+bool hyb_latent_norm_rope_cache(const void *proj, int64_t ld, const float *q_w, const float *kv_w, const float *freq, int64_t pairs,
+                                int32_t interleaved, const int64_t *positions, const int64_t *slots, void *cq_out, void *cache, int64_t T,
+                                int64_t q_rank, int64_t kv_rank, int64_t rot_dim, float eps, uint32_t dtype, cudaStream_t stream) {
+    if (T <= 0) return true;
+    if (!hybrid::known_dtype(dtype, "atoma_latent_norm_rope_cache")) return false;
+    if (!proj || kv_rank <= 0 || q_rank < 0 || rot_dim < 0 || ld < q_rank + kv_rank + rot_dim || !kv_w || (q_rank > 0 && (!q_w || !cq_out)) ||
+        (slots && !cache) || !positions || pairs < 0 || 2 * pairs > rot_dim || (pairs > 0 && !freq)) {
+        set_status(kErrInvalidArg, "atoma_latent_norm_rope_cache: null argument or a row shorter than q_rank + kv_rank + rot_dim");
+        return false;
+    }
+#define CALL(TT) launch_ex(latent_norm_rope_cache_kernel<TT>, dim3(static_cast<unsigned>(T)), dim3(kRowThreads), 0, stream, \
+                           static_cast<const TT *>(proj), ld, q_w, kv_w, freq, static_cast<int>(pairs), interleaved, positions, slots, \
+                           static_cast<TT *>(cq_out), static_cast<TT *>(cache), static_cast<int>(q_rank), static_cast<int>(kv_rank), \
+                           static_cast<int>(rot_dim), eps)
+    return hybrid::launched(HYB_DISPATCH(dtype, CALL), "latent_norm_rope_cache_kernel");
+#undef CALL
+}
+
+bool hyb_latent_query_absorb_rope(const void *q, const void *w_uk, const float *freq, int64_t pairs, int32_t interleaved,
+                                  const int64_t *positions, float *q_lat, int64_t T, int64_t H, int64_t dim, int64_t rot_dim, int64_t kv_rank,
+                                  uint32_t dtype, cudaStream_t stream) {
+    if (T <= 0) return true;
+    if (!hybrid::known_dtype(dtype, "atoma_latent_query_absorb_rope")) return false;
+    if (!q || !w_uk || !q_lat || !positions || H <= 0 || dim <= 0 || rot_dim < 0 || kv_rank <= 0 || pairs < 0 || 2 * pairs > rot_dim ||
+        (pairs > 0 && !freq)) {
+        set_status(kErrInvalidArg, "atoma_latent_query_absorb_rope: null argument or more rotated entries than the rotated part has");
+        return false;
+    }
+    const int64_t hs = dim + rot_dim, row = kv_rank + rot_dim;
+    if (!hyb_head_project_ld(q, H * hs, hs, w_uk, q_lat, H * row, row, T, H, dim, kv_rank, 1, dtype, stream)) return false;
+    if (rot_dim == 0) return true;
+#define CALL(TT) launch_ex(latent_query_rope_kernel<TT>, dim3(static_cast<unsigned>(T)), dim3(256), 0, stream, static_cast<const TT *>(q), freq, \
+                           static_cast<int>(pairs), interleaved, positions, q_lat, static_cast<int>(H), static_cast<int>(dim), \
+                           static_cast<int>(rot_dim), static_cast<int>(kv_rank))
+    return hybrid::launched(HYB_DISPATCH(dtype, CALL), "latent_query_rope_kernel");
+#undef CALL
+}
+
+bool hyb_latent_expand_values(const float *o_lat, const void *w_uv, void *out, int64_t T, int64_t H, int64_t vdim, int64_t kv_rank, int64_t row,
+                              uint32_t dtype, cudaStream_t stream) {
+    if (row < kv_rank) {
+        set_status(kErrInvalidArg, "atoma_latent_expand_values: rows of %lld entries for a latent of %lld", static_cast<long long>(row),
+                   static_cast<long long>(kv_rank));
+        return false;
+    }
+    return hyb_head_project_ld(o_lat, H * row, row, w_uv, out, H * vdim, vdim, T, H, vdim, kv_rank, 0, dtype, stream);
+}
+
+}  // namespace atoma
+
+using namespace atoma;
+
+extern "C" void atoma_parallel_residual_norm(const atoma_parallel_residual_args *args, atoma_stream_t stream) {
+    clear_status();
+    if (!args) {
+        set_status(kErrInvalidArg, "atoma_parallel_residual_norm: args is NULL");
+        return;
+    }
+    hyb_parallel_residual_norm(*args, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" void atoma_tap_filter(const atoma_tap_filter_args *args, atoma_stream_t stream) {
+    clear_status();
+    if (!args) {
+        set_status(kErrInvalidArg, "atoma_tap_filter: args is NULL");
+        return;
+    }
+    hyb_tap_filter(*args, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" void atoma_state_scan(const atoma_state_scan_args *args, atoma_stream_t stream) {
+    clear_status();
+    if (!args) {
+        set_status(kErrInvalidArg, "atoma_state_scan: args is NULL");
+        return;
+    }
+    hyb_state_scan(*args, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" void atoma_headnorm_gate(const float *o, const float *weight, const void *gate, int64_t ld_gate, void *out, int64_t T, int64_t H,
+                                    int64_t vdim, float eps, uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    hyb_headnorm_gate(o, weight, gate, ld_gate, out, T, H, vdim, eps, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" void atoma_qkv_headnorm_rope_cache(const atoma_qkv_rope_args *args, atoma_stream_t stream) {
+    clear_status();
+    if (!args) {
+        set_status(kErrInvalidArg, "atoma_qkv_headnorm_rope_cache: args is NULL");
+        return;
+    }
+    hyb_qkv_headnorm_rope_cache(*args, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" void atoma_rotate_heads(void *x, const int64_t *positions, const float *freq, int64_t T, int64_t H, int64_t n, int64_t pairs,
+                                   int32_t interleaved, float sign, uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    hyb_rotate_heads(x, positions, freq, T, H, n, pairs, interleaved, sign, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" void atoma_latent_norm_rope_cache(const void *proj, int64_t ld, const float *q_weight, const float *kv_weight, const float *freq,
+                                             int64_t pairs, int32_t interleaved, const int64_t *positions, const int64_t *slot_mapping,
+                                             void *cq_out, void *cache, int64_t T, int64_t q_rank, int64_t kv_rank, int64_t rot_dim, float eps,
+                                             uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    hyb_latent_norm_rope_cache(proj, ld, q_weight, kv_weight, freq, pairs, interleaved, positions, slot_mapping, cq_out, cache, T, q_rank, kv_rank,
+                               rot_dim, eps, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" void atoma_latent_query_absorb_rope(const void *q, const void *w_uk, const float *freq, int64_t pairs, int32_t interleaved,
+                                               const int64_t *positions, float *q_lat, int64_t T, int64_t H, int64_t dim, int64_t rot_dim,
+                                               int64_t kv_rank, uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    hyb_latent_query_absorb_rope(q, w_uk, freq, pairs, interleaved, positions, q_lat, T, H, dim, rot_dim, kv_rank, dtype,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+extern "C" void atoma_latent_expand_values(const float *o_lat, const void *w_uv, void *out, int64_t T, int64_t H, int64_t vdim, int64_t kv_rank,
+                                           int64_t row, uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    hyb_latent_expand_values(o_lat, w_uv, out, T, H, vdim, kv_rank, row, dtype, static_cast<cudaStream_t>(stream));
+}

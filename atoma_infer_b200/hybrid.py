@@ -28,6 +28,18 @@ Designs on residual lanes (block_style "lanes"):
   dense: w_gate_up [2 ff, width], b_gate_up [2 ff], w_down [width, ff], b_down [width]
   experts: w_router [experts + identity, width] float32, router_correction [same], w_expert_gate_up, w_expert_down,
            shared expert w_ff_in [2 shared_ff, width], w_down [width, shared_ff]
+Parallel blocks (block_style "parallel": one norm per layer, x += mixer(f1(h)) + ff(f2(h)) with causal tap filters f1, f2):
+  norm1 [width]   tap_w1, tap_w2 [width, taps] float32   w_gate_up [2 ff, width]   w_down [width, ff]
+  gated linear attention: w_q, w_k [H dim, width], w_v, w_g [H vdim, width], w_a1 [rank, width], w_a2 [H dim, rank], a2_bias [H dim],
+                          head_norm [vdim], w_o [width, H vdim]
+  latent attention with a rotated key part: w_dq [q_rank, width], w_dkv [kv_rank + rot_dim, width], dq_norm, dkv_norm, w_uq
+                          [H (dim + rot_dim), q_rank], w_uk [H dim, kv_rank], w_uv [H vdim, kv_rank], w_o [width, H vdim]
+  pair of mixers: left  w_q [H dim, width], w_k [G dim, width], w_v [G vdim, width], q_norm, k_norm [dim], head_bias [H], w_o
+                  right r_w_q, r_w_k [G' dim', width], r_w_v, r_w_g [H' vdim', width], r_w_b, r_w_a [H', width], r_tap_q / r_tap_k / r_tap_v
+                        [channels, taps'], r_a_log, r_dt_bias [H'], r_head_norm [vdim'], r_w_o [width, H' vdim']
+                  out_norm_a, out_norm_b [width]
+  the model: pass_vectors [passes, width] float32 (the vector added at the start of every pass over a looped span)
+The executor stacks the projections that read the same input into one matrix (rows padded to a multiple of 8).
 """
 from __future__ import annotations
 
@@ -45,10 +57,10 @@ from .ops import AtomaError
 from .scheduler import StepPlan
 from .worker import InputStager, SequenceInput
 
-MIXER_ATTENTION, MIXER_MINGRU, MIXER_LATENT, MIXER_SOFTMAX = 0, 1, 2, 3
+MIXER_ATTENTION, MIXER_MINGRU, MIXER_LATENT, MIXER_SOFTMAX, MIXER_GLA, MIXER_PAIR = 0, 1, 2, 3, 4, 5
 LONG_PORTION = 128        # tokens of a sequence in one step from which attention runs on the tensor-memory prefill kernel
                           # (latent attention: on expanded keys and values; softmax attention: on gathered ones)
-BLOCK_STYLES = {"sandwich": 0, "prenorm": 1, "lanes": 2}
+BLOCK_STYLES = {"sandwich": 0, "prenorm": 1, "lanes": 2, "parallel": 3}
 SCORE_FNS = {"sigmoid": 0, "softmax": 1}
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
 DTYPE_CODES = {torch.bfloat16: 1, torch.float32: 2}
@@ -89,6 +101,8 @@ class LatentAttentionSpec:
     scale: float
     window: int = 0                # 0 = every earlier token is visible
     sink: bool = False             # a learned per-head term of the softmax denominator
+    rot_dim: int = 0               # parallel blocks: rotated entries per query head and of the one key part all heads share
+    rotary: Optional["RotarySpec"] = None
 
 
 @dataclass(frozen=True)
@@ -105,6 +119,75 @@ class SoftmaxAttentionSpec:
     values_are_keys: bool = False  # no value projection: the values are the key projections before their norm
     out_gate: bool = False         # heads' outputs times sigmoid(W h) before the output projection
     distance_bias: bool = False    # weights carry dist_bias [rows, heads]
+
+
+@dataclass(frozen=True)
+class RotarySpec:
+    """Rotary positions on the first `dims` entries of a head: pair i turns by position * base^(-2 i / dims).  `scaling`
+    (factor, low, high, original) stretches long wavelengths: a wavelength below original / high keeps its frequency, one
+    above original / low has it divided by factor, and in between the two are blended linearly in original / wavelength."""
+    dims: int
+    base: float = 10000.0
+    interleaved: bool = False                 # pairs (2i, 2i + 1) instead of (i, i + dims / 2)
+    scaling: Optional[Seq_[float]] = None     # (factor, low, high, original)
+
+    def frequencies(self) -> List[float]:
+        out = []
+        for i in range(self.dims // 2):
+            f = float(self.base) ** (-2.0 * i / self.dims)
+            if self.scaling is not None:
+                factor, low, high, original = (float(v) for v in self.scaling)
+                wave = 2.0 * math.pi / f
+                if wave > original / low:
+                    f = f / factor
+                elif wave >= original / high:
+                    t = (original / wave - low) / (high - low)
+                    f = (1.0 - t) * f / factor + t * f
+            out.append(f)
+        return out
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """A [dim, vdim] state per head whose rows decay by sigmoid(z)^(1 / tau) per key channel, z through a low-rank pair of
+    projections; the read-out is RMS-normed per head and gated by silu(W_g h)."""
+    heads: int
+    dim: int
+    vdim: int
+    decay_rank: int
+    tau: float = 16.0
+
+
+@dataclass(frozen=True)
+class RotarySigmoidAttentionSpec:
+    """Sigmoid attention (weights sigmoid(score + per-head bias), not normalised) with a per-head q/k RMS norm, rotary
+    positions on queries and keys, and values that are turned by their own position over all of vdim when cached; a head's
+    sum is turned back by the query's position."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rotary: Optional[RotarySpec] = None
+    rotate_values: bool = True
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """Gated delta rule: short causal filters with silu on q / k / v, unit-length q and k, write strength sigmoid(W_b h) and decay
+    exp(-exp(A_log) softplus(W_a h + dt_bias)) per head, read-out RMS-normed per head and gated by silu(W_g h)."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    taps: int = 4
+
+
+@dataclass(frozen=True)
+class MixerPairSpec:
+    """Two mixers on the same input; each result is RMS-normed over the model width and the two are averaged."""
+    left: RotarySigmoidAttentionSpec
+    right: DeltaRuleSpec
 
 
 @dataclass(frozen=True)
@@ -153,6 +236,11 @@ class LayerSpec:
     gated_residual: bool = False             # sublayer results times sigmoid(W h + b) before they join the stream
     side_part: Optional[int] = None          # which part of the token side table the layer reads; None = no side input
     source: Optional[int] = None             # entry of weights["layers"] the run uses; None = its own index
+    gla: Optional["GatedLinearAttentionSpec"] = None
+    pair: Optional["MixerPairSpec"] = None
+    taps: int = 0                            # parallel blocks: taps of the filters on the sublayers' inputs (<= 1: none)
+    add_embedding: bool = False              # parallel blocks: the embedding rows are added to the stream before the layer
+    pass_vector: Optional[int] = None        # ... and this row of weights["pass_vectors"]
 
 
 @dataclass(frozen=True)
@@ -175,13 +263,14 @@ class HybridSpec:
 
     @property
     def has_state(self) -> bool:
-        return any(l.mixer == "mingru" for l in self.layers)
+        return any(l.mixer == "mingru" or l.taps > 1 or l.gla is not None or l.pair is not None for l in self.layers)
 
     def cache_bytes_per_token(self, dtype: torch.dtype) -> int:
         es = torch.empty((), dtype=dtype).element_size()
         return (sum(l.attention.kv_heads * (l.attention.dim + l.attention.vdim) * es for l in self.layers if l.mixer == "attention") +
                 sum(l.softmax.kv_heads * (l.softmax.dim + l.softmax.vdim) * es for l in self.layers if l.mixer == "softmax_attention") +
-                sum(l.latent.kv_rank * es for l in self.layers if l.mixer == "latent_attention"))
+                sum((l.latent.kv_rank + l.latent.rot_dim) * es for l in self.layers if l.mixer == "latent_attention") +
+                sum(l.pair.left.kv_heads * (l.pair.left.dim + l.pair.left.vdim) * es for l in self.layers if l.pair is not None))
 
 
 @dataclass
@@ -224,6 +313,8 @@ class HybridExecutor:
         if spec.block_style == "lanes":
             if not 1 <= spec.lanes <= 16:
                 raise AtomaError(f"{spec.lanes} residual lanes (1 to 16 are supported)")
+        elif spec.block_style == "parallel":
+            pass                  # positions enter through the mixers' rotations
         elif spec.position == "learned":
             self.pos_table = big(weights["pos"])
             if self.pos_table.shape[0] < spec.max_positions or spec.max_positions <= 0:
@@ -259,6 +350,14 @@ class HybridExecutor:
                 self.v_caches.append(vc)
                 self.states.append(None)
                 self.latent_caches.append(None)
+                continue
+            if spec.block_style == "parallel":
+                if src in placed:
+                    C.memmove(C.byref(L), C.byref(placed[src]), C.sizeof(HybridLayer))     # same weights; caches, state and pass start below
+                else:
+                    self._place_parallel(L, i, ls, w, big, small)
+                    placed[src] = L
+                self._parallel_run_state(L, i, ls, weights, small, rows)
                 continue
             if spec.block_style == "prenorm":
                 if src in placed:
@@ -436,6 +535,174 @@ class HybridExecutor:
         L.w_expert_gate_up, L.w_expert_down = big(w["w_expert_gate_up"]).data_ptr(), big(w["w_expert_down"]).data_ptr()
         if e.shared_ff > 0:
             L.w_ff_in, L.w_down = big(w["w_ff_in"]).data_ptr(), big(w["w_down"]).data_ptr()
+
+    def _place_parallel(self, L, i: int, ls: LayerSpec, w: dict, big, small) -> None:
+        """Device copies and sizes of one parallel layer: the projections that read the mixer's input stacked into one matrix
+        (every part starts at a multiple of 8 rows, so that each has 16-byte aligned columns in the product)."""
+        W = self.spec.width
+
+        def need(name, shape):
+            t = w.get(name)
+            if t is None or tuple(t.shape) != tuple(shape):
+                raise AtomaError(f"layer {i}: tensor {name} is {None if t is None else tuple(t.shape)}, the description needs {tuple(shape)}")
+            return t
+
+        parts: List[torch.Tensor] = []
+        offsets: Dict[str, int] = {}
+
+        def stack(key, name, rows):
+            t = need(name, (rows, W))
+            offsets[key] = sum(p.shape[0] for p in parts)
+            parts.append(t)
+            pad = -rows % 8
+            if pad:
+                parts.append(torch.zeros((pad, W), dtype=t.dtype))
+
+        L.norm1 = small(need("norm1", (W,))).data_ptr()
+        L.taps = max(0, int(ls.taps))
+        if ls.taps > 16:
+            raise AtomaError(f"layer {i}: {ls.taps} taps (at most 16 are supported)")
+        if ls.taps > 1:
+            L.tap_w1 = small(need("tap_w1", (W, ls.taps))).data_ptr()
+        f = ls.mlp
+        L.has_mlp = 1 if f is not None else 0
+        if f is not None:
+            if f.act not in ACTIVATIONS:
+                raise AtomaError(f"layer {i}: unknown activation {f.act!r}")
+            L.ff, L.act = f.ff, ACTIVATIONS[f.act]
+            L.w_gate_up, L.w_down = big(need("w_gate_up", (2 * f.ff, W))).data_ptr(), big(need("w_down", (W, f.ff))).data_ptr()
+            if ls.taps > 1:
+                L.tap_w2 = small(need("tap_w2", (W, ls.taps))).data_ptr()
+        if ls.mixer == "gla":
+            a = ls.gla
+            L.mixer = MIXER_GLA
+            L.heads, L.kv_heads, L.dim, L.vdim, L.tau, L.scale = a.heads, a.heads, a.dim, a.vdim, a.tau, a.dim ** -0.5
+            if not a.tau > 0:
+                raise AtomaError(f"layer {i}: tau must be positive, got {a.tau}")
+            stack("q", "w_q", a.heads * a.dim)
+            stack("k", "w_k", a.heads * a.dim)
+            stack("v", "w_v", a.heads * a.vdim)
+            stack("g", "w_g", a.heads * a.vdim)
+            L.proj_cols = sum(p.shape[0] for p in parts)
+            stack("a", "w_a1", a.decay_rank)              # behind the stacked product's rows: a product of its own
+            L.q_off, L.k_off, L.v_off, L.g_off, L.a_off = (offsets[k] for k in "qkvga")
+            L.a_rank = a.decay_rank
+            L.w_a2 = big(need("w_a2", (a.heads * a.dim, a.decay_rank))).data_ptr()
+            L.a2_bias = small(need("a2_bias", (a.heads * a.dim,))).data_ptr()
+            L.head_norm = small(need("head_norm", (a.vdim,))).data_ptr()
+            L.w_o = big(need("w_o", (W, a.heads * a.vdim))).data_ptr()
+        elif ls.mixer == "latent_attention":
+            a = ls.latent
+            L.mixer = MIXER_LATENT
+            L.heads, L.kv_heads, L.dim, L.vdim = a.heads, 1, a.dim, a.vdim
+            L.q_rank, L.kv_rank, L.window, L.scale, L.rot_dim = a.q_rank, a.kv_rank, a.window, a.scale, a.rot_dim
+            if a.q_rank % 8:
+                raise AtomaError(f"layer {i}: a query latent of {a.q_rank} entries (a multiple of 8 is needed)")
+            stack("dq", "w_dq", a.q_rank)
+            stack("dkv", "w_dkv", a.kv_rank + a.rot_dim)      # follows the query latent directly: q_rank is a multiple of 8
+            L.proj_cols = sum(p.shape[0] for p in parts)
+            L.dq_norm, L.dkv_norm = small(need("dq_norm", (a.q_rank,))).data_ptr(), small(need("dkv_norm", (a.kv_rank,))).data_ptr()
+            L.w_uq = big(need("w_uq", (a.heads * (a.dim + a.rot_dim), a.q_rank))).data_ptr()
+            L.w_uk = big(need("w_uk", (a.heads * a.dim, a.kv_rank))).data_ptr()
+            L.w_uv = big(need("w_uv", (a.heads * a.vdim, a.kv_rank))).data_ptr()
+            L.w_o = big(need("w_o", (W, a.heads * a.vdim))).data_ptr()
+            if a.rot_dim > 0:
+                r = a.rotary or RotarySpec(dims=a.rot_dim)
+                if r.dims > a.rot_dim or r.dims % 2:
+                    raise AtomaError(f"layer {i}: {r.dims} rotated entries in a part of {a.rot_dim}")
+                L.qk_freq, L.rot_pairs, L.rot_interleaved = small(torch.tensor(r.frequencies(), dtype=torch.float64)).data_ptr(), r.dims // 2, int(r.interleaved)
+        elif ls.mixer == "pair":
+            a, d = ls.pair.left, ls.pair.right
+            L.mixer = MIXER_PAIR
+            if a.heads % a.kv_heads or d.heads % d.kv_heads:
+                raise AtomaError(f"layer {i}: key/value heads ({a.kv_heads}, {d.kv_heads}) must divide the heads ({a.heads}, {d.heads})")
+            L.heads, L.kv_heads, L.dim, L.vdim, L.scale = a.heads, a.kv_heads, a.dim, a.vdim, a.scale
+            stack("q", "w_q", a.heads * a.dim)
+            stack("k", "w_k", a.kv_heads * a.dim)
+            stack("v", "w_v", a.kv_heads * a.vdim)
+            # the filtered columns q, k, v of the right mixer are neighbours: padding only after the three
+            rq = need("r_w_q", (d.kv_heads * d.dim, W))
+            rk = need("r_w_k", (d.kv_heads * d.dim, W))
+            rv = need("r_w_v", (d.heads * d.vdim, W))
+            offsets["rq"] = sum(p.shape[0] for p in parts)
+            offsets["rk"], offsets["rv"] = offsets["rq"] + rq.shape[0], offsets["rq"] + rq.shape[0] + rk.shape[0]
+            parts.extend([rq, rk, rv])
+            pad = -(rq.shape[0] + rk.shape[0] + rv.shape[0]) % 8
+            if pad:
+                parts.append(torch.zeros((pad, W), dtype=rq.dtype))
+            stack("rg", "r_w_g", d.heads * d.vdim)
+            stack("rb", "r_w_b", d.heads)
+            stack("ra", "r_w_a", d.heads)
+            L.proj_cols = sum(p.shape[0] for p in parts)
+            L.q_off, L.k_off, L.v_off = offsets["q"], offsets["k"], offsets["v"]
+            L.rq_off, L.rk_off, L.rv_off, L.rg_off, L.rb_off, L.ra_off = (offsets[k] for k in ("rq", "rk", "rv", "rg", "rb", "ra"))
+            L.q_norm, L.k_norm = small(need("q_norm", (a.dim,))).data_ptr(), small(need("k_norm", (a.dim,))).data_ptr()
+            L.head_bias = small(need("head_bias", (a.heads,))).data_ptr()
+            L.slopes = small(torch.zeros(a.heads)).data_ptr()
+            L.w_o = big(need("w_o", (W, a.heads * a.vdim))).data_ptr()
+            if a.rotary is not None:
+                r = a.rotary
+                if r.dims > a.dim or r.dims % 2:
+                    raise AtomaError(f"layer {i}: {r.dims} rotated entries in a head of {a.dim}")
+                L.qk_freq, L.rot_pairs, L.rot_interleaved = small(torch.tensor(r.frequencies(), dtype=torch.float64)).data_ptr(), r.dims // 2, int(r.interleaved)
+                if a.rotate_values:
+                    if a.vdim % 2:
+                        raise AtomaError(f"layer {i}: rotated values need an even vdim, got {a.vdim}")
+                    fv = RotarySpec(dims=a.vdim, base=r.base, interleaved=r.interleaved).frequencies()
+                    L.v_freq, L.v_pairs = small(torch.tensor(fv, dtype=torch.float64)).data_ptr(), a.vdim // 2
+            if not 1 <= d.taps <= 16:
+                raise AtomaError(f"layer {i}: {d.taps} taps of the short filters (1 to 16 are supported)")
+            L.r_heads, L.r_kv_heads, L.r_dim, L.r_vdim, L.r_taps = d.heads, d.kv_heads, d.dim, d.vdim, d.taps
+            L.r_tap_w = small(torch.cat([need("r_tap_q", (d.kv_heads * d.dim, d.taps)), need("r_tap_k", (d.kv_heads * d.dim, d.taps)),
+                                         need("r_tap_v", (d.heads * d.vdim, d.taps))], 0)).data_ptr()
+            L.r_a_log, L.r_dt_bias = small(need("r_a_log", (d.heads,))).data_ptr(), small(need("r_dt_bias", (d.heads,))).data_ptr()
+            L.r_head_norm = small(need("r_head_norm", (d.vdim,))).data_ptr()
+            L.r_w_o = big(need("r_w_o", (W, d.heads * d.vdim))).data_ptr()
+            L.out_norm_a, L.out_norm_b = small(need("out_norm_a", (W,))).data_ptr(), small(need("out_norm_b", (W,))).data_ptr()
+        else:
+            raise AtomaError(f"layer {i}: parallel blocks take the mixers gla, latent_attention and pair, not {ls.mixer!r}")
+        L.w_qkv = big(torch.cat(parts, 0)).data_ptr()
+
+    def state_floats(self, ls: LayerSpec) -> int:
+        """float32 entries of one sequence's state in one run of a parallel layer: [input history | mixer state]."""
+        n = max(0, ls.taps - 1) * self.spec.width
+        if ls.gla is not None:
+            n += ls.gla.heads * ls.gla.dim * ls.gla.vdim
+        if ls.pair is not None:
+            d = ls.pair.right
+            n += max(0, d.taps - 1) * (2 * d.kv_heads * d.dim + d.heads * d.vdim) + d.heads * d.dim * d.vdim
+        return n
+
+    def _parallel_run_state(self, L, i: int, ls: LayerSpec, weights: dict, small, rows: int) -> None:
+        """What one RUN of a parallel layer owns: its caches, its state rows, and what precedes it in the stream."""
+        dev, dtype = self.device, self.dtype
+        kc = vc = lc = st = None
+        if ls.mixer == "latent_attention":
+            lc = torch.zeros((rows, ls.latent.kv_rank + ls.latent.rot_dim), dtype=dtype, device=dev)
+            L.latent_cache = lc.data_ptr()
+        elif ls.mixer == "pair":
+            a = ls.pair.left
+            kc = torch.zeros((rows, a.kv_heads, a.dim), dtype=dtype, device=dev)
+            vc = torch.zeros((rows, a.kv_heads, a.vdim), dtype=dtype, device=dev)
+            L.k_cache, L.v_cache = kc.data_ptr(), vc.data_ptr()
+        n = self.state_floats(ls)
+        if n > 0:
+            st = torch.zeros((max(1, self.num_state_slots), n), dtype=torch.float32, device=dev)
+            L.layer_state, L.layer_state_stride = st.data_ptr(), n
+        else:
+            L.layer_state, L.layer_state_stride = None, 0
+        L.add_embedding = int(ls.add_embedding)
+        if ls.pass_vector is not None:
+            pv = weights.get("pass_vectors")
+            if pv is None or pv.dim() != 2 or pv.shape[1] != self.spec.width or not 0 <= ls.pass_vector < pv.shape[0]:
+                raise AtomaError(f"layer run {i}: pass vector {ls.pass_vector} of a table {None if pv is None else tuple(pv.shape)}")
+            L.add_vec = small(pv[ls.pass_vector]).data_ptr()
+        else:
+            L.add_vec = None
+        self.k_caches.append(kc)
+        self.v_caches.append(vc)
+        self.latent_caches.append(lc)
+        self.states.append(st)
 
     # ---- buffers (grow-only) ----
     def _reserve(self, T: int, S: int) -> None:

@@ -79,6 +79,14 @@ def _build_nemasun(cfg, ckpt, dtype, device, cache: CacheConfig):
     return HybridExecutor(spec, weights, dtype, device, cache.num_blocks, cache.block_size, cache.num_state_slots)
 
 
+def _build_surinex(cfg, ckpt, dtype, device, cache: CacheConfig):
+    from . import surinex
+    from .hybrid import HybridExecutor
+    spec = surinex.spec_from_config(cfg, {k: tuple(v.shape) for k, v in ckpt.items()})
+    weights = surinex.weights_from_checkpoint(spec, cfg, ckpt)
+    return HybridExecutor(spec, weights, dtype, device, cache.num_blocks, cache.block_size, cache.num_state_slots)
+
+
 def _build_llama(cfg, ckpt, dtype, device, cache: CacheConfig):
     from .llama_engine import LlamaExecutor
     return LlamaExecutor.from_checkpoint(cfg, ckpt, dtype, device, cache)
@@ -87,4 +95,5 @@ def _build_llama(cfg, ckpt, dtype, device, cache: CacheConfig):
 register_model("Lilovik", _build_lilovik, _lilovik_needs_state)
 register_model("Patadra", _build_patadra)
 register_model("Nemasun", _build_nemasun)
+register_model("Surinex", _build_surinex, lambda cfg: True)       # input histories of the tap filters, in every layer
 register_model("LlamaForCausalLM", _build_llama)

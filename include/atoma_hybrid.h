@@ -29,6 +29,16 @@
  * per-output correction and is restricted to the best groups of neighbouring outputs, with identity
  * experts (router outputs that hand the token's input through) and an ungated shared expert.
  *
+ * The fourth design is Surinex: PARALLEL blocks (one RMS norm per layer whose output both the mixer and the
+ * feed-forward read, each through its own causal tap filter over time whose last inputs are carried as state;
+ * x <- x + mixer + feed-forward), three mixers — gated linear attention (a matrix state per head whose rows decay
+ * by a data-dependent factor per key channel), latent attention with one rotated key part shared by all heads
+ * beside the cached latent, and a PAIR of mixers on the same input: sigmoid attention with rotary positions on
+ * queries, keys AND values (a head's sum is turned back by the query's position) beside a gated delta rule
+ * (short causal filters with silu on q / k / v, unit-length q and k, a scalar decay and a write strength per
+ * head), each result RMS-normed over the model width before the two are averaged — and a span of layers that
+ * runs several times with the embedding added again and a per-pass vector at the start of every pass.
+ *
  * Conventions: row-major; `dtype` is the number format of activations, large weights and the caches:
  * 1 = bfloat16, 2 = float32 (true 32-bit arithmetic: no reduced-precision matrix mode).  Whatever the
  * dtype, the residual stream, norm statistics, attention scores and weights, recurrent state and all
@@ -389,10 +399,148 @@ void atoma_glu_clamped_bias(const void *gu, int64_t ld, const float *bias, void 
                             float up_shift, uint32_t dtype, atoma_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------ */
+/* Parallel blocks: tap filters with carried inputs, matrix-state recurrences, rotary operators */
+/* ------------------------------------------------------------------------------------------ */
+
+/*
+ * Residual update of a parallel block fused with what precedes the next layer and with that layer's input norm.
+ * Per token t and channel c, all in float32:
+ *   a = y_a ? (norm_a ? y_a[t, :] / sqrt(mean(y_a[t, :]^2) + eps) * norm_a : y_a[t, :]) : 0        (b likewise)
+ *   x[t, c] += mix_scale * (a[c] + b[c]) + (y_ff ? y_ff[t, c] : 0);     trace[t, c] = x[t, c]          (trace NULL: not written)
+ *   x[t, c] += (add_rows ? add_rows[t, c] : 0) + (add_vec ? add_vec[c] : 0)
+ *   h[t, :]  = x[t, :] / sqrt(mean(x[t, :]^2) + eps) * (weight_offset + w_next)                       (w_next NULL: no norm)
+ * y_a, y_b, y_ff, h in `dtype` [T, width]; x, trace, add_rows float32 [T, width].  With no addends it is the first
+ * layer's input norm.
+ */
+typedef struct atoma_parallel_residual_args {
+    const void *y_a, *y_b, *y_ff;
+    const float *norm_a, *norm_b; /* [width] or NULL */
+    float mix_scale;
+    float *x;
+    float *trace;
+    const float *add_rows, *add_vec;
+    const float *w_next;
+    void *h;
+    int64_t T, width;
+    float eps, weight_offset;
+    uint32_t dtype;
+} atoma_parallel_residual_args;
+void atoma_parallel_residual_norm(const atoma_parallel_residual_args *args, atoma_stream_t stream);
+
+/*
+ * Causal tap filter over time per channel, on a mixed batch, with the inputs that precede a portion carried as state.
+ * in [T, channels] (row stride ld_in, `dtype`); w1, w2 [channels, taps] float32, the LAST column weighs the current token
+ * (w2 / out2 may be NULL: one filter).  For token t of sequence b at position p:
+ *   f_k(t, c) = sum_{j < taps} w_k[c, j] * in(position p - (taps - 1) + j, c)       zero before the sequence's start
+ *   out_k[t, c] = act(residual ? in[t, c] + f_k : f_k)        act: 0 = none, 1 = silu        (`dtype`, row stride ld_out)
+ * history [slots, history_stride] float32 holds, at the slot of the sequence, its last taps - 1 inputs as
+ * [taps - 1, channels]; it is read for positions before the portion (never when they lie before the sequence's start)
+ * and rewritten with the portion's last inputs.  taps <= 16.
+ */
+typedef struct atoma_tap_filter_args {
+    const void *in;
+    int64_t ld_in;
+    const float *w1, *w2;
+    void *out1, *out2;
+    int64_t ld_out;
+    float *history;
+    int64_t history_stride;
+    const int32_t *state_slots;   /* [B] */
+    const int32_t *token_seq;     /* [T] */
+    const int32_t *query_start;   /* [B + 1] */
+    const int32_t *context_lens;  /* [B] */
+    int64_t T, B, channels, taps;
+    int32_t residual, act;
+    uint32_t dtype;
+} atoma_tap_filter_args;
+void atoma_tap_filter(const atoma_tap_filter_args *args, atoma_stream_t stream);
+
+/*
+ * Matrix-state recurrences on a mixed batch.  Every head keeps S [dim, vdim] float32 at the sequence's state slot
+ * (state [slots, state_stride], head h at h dim vdim); it starts from zero when context_lens[b] == 0 and is stored back.
+ * Tokens of a sequence are visited in order, so the result does not depend on how the sequence was cut into steps.
+ *   kind 0, gated linear attention (q, k [T, H dim], v [T, H vdim]; decay pre-activation z [T, H dim] + z_bias):
+ *     alpha = exp(log(sigmoid(z)) / tau);  S <- diag(alpha) S + k v^T;  o = S^T (q * q_scale)
+ *   kind 1, gated delta rule (q, k [T, G dim] shared by H / G heads, v [T, H vdim]; per head b_pre, a_pre [T, H]):
+ *     q, k <- x / sqrt(sum(x^2) + unit_eps) (q also times q_scale);  beta = sigmoid(b_pre);
+ *     g = exp(-exp(a_log[h]) * softplus(a_pre + dt_bias[h]));
+ *     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+ * q, k, v, z, b_pre, a_pre are columns of `dtype` matrices with their own row strides; out float32 [T, H vdim].
+ */
+typedef struct atoma_state_scan_args {
+    int32_t kind;
+    const void *q, *k, *v, *z, *b_pre, *a_pre;
+    int64_t ld_q, ld_k, ld_v, ld_z, ld_b, ld_a;
+    const float *z_bias;          /* [H dim] (kind 0) */
+    const float *a_log, *dt_bias; /* [H] (kind 1) */
+    float tau, q_scale, unit_eps;
+    float *state;
+    int64_t state_stride;
+    const int32_t *state_slots, *query_start, *context_lens;
+    float *out;
+    int64_t T, B, H, G, dim, vdim;
+    uint32_t dtype;
+} atoma_state_scan_args;
+void atoma_state_scan(const atoma_state_scan_args *args, atoma_stream_t stream);
+
+/* out[t, h vdim + j] = o[t, h, j] / sqrt(mean_j(o[t, h, :]^2) + eps) * weight[j] * silu(gate[t, h vdim + j]);
+ * o float32 [T, H vdim], gate (row stride ld_gate) and out [T, H vdim] in `dtype`; gate NULL: no gate. */
+void atoma_headnorm_gate(const float *o, const float *weight, const void *gate, int64_t ld_gate, void *out, int64_t T, int64_t H,
+                         int64_t vdim, float eps, uint32_t dtype, atoma_stream_t stream);
+
+/*
+ * After a fused projection proj[t, :] (row stride ld): queries at q_off (H heads of dim), keys at k_off (G of dim), values
+ * at v_off (G of vdim).  Per head: RMS norm over dim with q_weight / k_weight ([dim], NULL: none), then the first
+ * 2 rot_pairs entries are turned by position * qk_freq[i] (float32 angle) in pairs (2i, 2i + 1) (interleaved = 1) or
+ * (i, i + rot_pairs) (0); the values' first 2 v_pairs entries likewise by v_freq (v_freq NULL: stored as projected).
+ * q -> q_out [T, H dim]; k, v -> cache rows slot_mapping[t] (slot < 0 is skipped).
+ */
+typedef struct atoma_qkv_rope_args {
+    const void *proj;
+    int64_t ld, q_off, k_off, v_off;
+    const float *q_weight, *k_weight;
+    const float *qk_freq, *v_freq;
+    int64_t rot_pairs, v_pairs;
+    int32_t interleaved;
+    const int64_t *positions, *slot_mapping;
+    void *q_out, *k_cache, *v_cache;
+    int64_t T, H, G, dim, vdim;
+    float eps;
+    uint32_t dtype;
+} atoma_qkv_rope_args;
+void atoma_qkv_headnorm_rope_cache(const atoma_qkv_rope_args *args, atoma_stream_t stream);
+
+/* In place on x [T, H, n] (`dtype`): the first 2 pairs entries of every head turned by sign * position * freq[i]. */
+void atoma_rotate_heads(void *x, const int64_t *positions, const float *freq, int64_t T, int64_t H, int64_t n, int64_t pairs,
+                        int32_t interleaved, float sign, uint32_t dtype, atoma_stream_t stream);
+
+/*
+ * Latent attention with a rotated key part.  proj[t, :] (row stride ld) = [c_q (q_rank) | c (kv_rank) | k_rot (rot_dim)]:
+ *   cq_out[t, :] = rms(c_q) * q_weight;   cache[slot_mapping[t], :] = [rms(c) * kv_weight | rotate(k_rot, position)]
+ * rotation in pairs (i, i + pairs) (interleaved 0) or (2i, 2i + 1); cache rows of kv_rank + rot_dim in `dtype`.
+ */
+void atoma_latent_norm_rope_cache(const void *proj, int64_t ld, const float *q_weight, const float *kv_weight, const float *freq,
+                                  int64_t pairs, int32_t interleaved, const int64_t *positions, const int64_t *slot_mapping,
+                                  void *cq_out, void *cache, int64_t T, int64_t q_rank, int64_t kv_rank, int64_t rot_dim, float eps,
+                                  uint32_t dtype, atoma_stream_t stream);
+
+/* Queries q [T, H, dim + rot_dim] (`dtype`) into the space of the cached rows, q_lat float32 [T, H, kv_rank + rot_dim]:
+ *   q_lat[t, h, :kv_rank] = w_uk_h^T q[t, h, :dim]  (w_uk [H dim, kv_rank]);   q_lat[t, h, kv_rank:] = rotate(q[t, h, dim:], position) */
+void atoma_latent_query_absorb_rope(const void *q, const void *w_uk, const float *freq, int64_t pairs, int32_t interleaved,
+                                    const int64_t *positions, float *q_lat, int64_t T, int64_t H, int64_t dim, int64_t rot_dim,
+                                    int64_t kv_rank, uint32_t dtype, atoma_stream_t stream);
+
+/* Values of every head from its weighted sum of cached rows: out[t, h vdim + j] = sum_{r < kv_rank} o_lat[t, h, r] w_uv[h vdim + j, r];
+ * o_lat float32 [T, H, row] with row >= kv_rank (what lies behind kv_rank is not read). */
+void atoma_latent_expand_values(const float *o_lat, const void *w_uv, void *out, int64_t T, int64_t H, int64_t vdim, int64_t kv_rank,
+                                int64_t row, uint32_t dtype, atoma_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------ */
 /* Step executor                                                                                */
 /* ------------------------------------------------------------------------------------------ */
-enum { ATOMA_MIXER_SIGMOID_ATTENTION = 0, ATOMA_MIXER_MINGRU = 1, ATOMA_MIXER_LATENT_ATTENTION = 2, ATOMA_MIXER_SOFTMAX_ATTENTION = 3 };
-enum { ATOMA_BLOCK_SANDWICH = 0, ATOMA_BLOCK_PRENORM = 1, ATOMA_BLOCK_LANES = 2 };
+enum { ATOMA_MIXER_SIGMOID_ATTENTION = 0, ATOMA_MIXER_MINGRU = 1, ATOMA_MIXER_LATENT_ATTENTION = 2, ATOMA_MIXER_SOFTMAX_ATTENTION = 3,
+       ATOMA_MIXER_GLA = 4, ATOMA_MIXER_PAIR = 5 };
+enum { ATOMA_BLOCK_SANDWICH = 0, ATOMA_BLOCK_PRENORM = 1, ATOMA_BLOCK_LANES = 2, ATOMA_BLOCK_PARALLEL = 3 };
 enum { ATOMA_SCORE_SIGMOID = 0, ATOMA_SCORE_SOFTMAX = 1 };
 enum { ATOMA_FF_DENSE = 0, ATOMA_FF_MOE = 1 };
 enum { ATOMA_ACT_SILU = 0, ATOMA_ACT_RELU = 1, ATOMA_ACT_GELU_TANH = 2 };
@@ -453,6 +601,37 @@ typedef struct atoma_hybrid_layer {
     const float *router_correction;  /* [experts + identity_experts] or NULL */
     int64_t route_groups, route_keep, identity_experts;
     int32_t score_fn, scale_input;   /* ATOMA_SCORE_*; 1: the router's weight scales the expert's input, 0: its output */
+    /* ---- parallel blocks (model.block_style = ATOMA_BLOCK_PARALLEL): x += mixer(f1(h)) + ff(f2(h)), h = norm1(x) ---- */
+    /* what precedes the layer: the embedding rows and / or a vector added to the stream (the start of a pass over a looped span) */
+    int32_t add_embedding;
+    const float *add_vec;            /* [width] or NULL */
+    /* tap filters of the two sublayers' inputs (taps <= 1: none); the layer's state row = [input history | mixer state] */
+    int64_t taps;
+    const float *tap_w1, *tap_w2;    /* [width, taps] */
+    float *layer_state;              /* [slots, layer_state_stride] float32 */
+    int64_t layer_state_stride;
+    /* stacked projection of the mixer: w_qkv [proj_cols, width]; columns of its parts (-1: absent) */
+    int64_t proj_cols;
+    /* gated linear attention (heads, dim, vdim): q, k, v, g columns, the decay's low-rank projection (w_a1 [a_rank, width] as
+     * columns a_off .. of the stacked projection, w_a2 [heads dim, a_rank], bias), head norm weight, tau */
+    int64_t q_off, k_off, v_off, g_off, a_off, a_rank;
+    const void *w_a2;
+    const float *a2_bias, *head_norm;
+    float tau;
+    /* pair of mixers: left = sigmoid attention with rotary positions (heads, kv_heads, dim, vdim, scale, q_norm, k_norm, head_bias,
+     * k_cache, v_cache, w_o above), right = gated delta rule */
+    const float *qk_freq, *v_freq;   /* [rot_pairs], [v_pairs] float32 */
+    int64_t rot_pairs, v_pairs;
+    int32_t rot_interleaved;
+    int64_t r_heads, r_kv_heads, r_dim, r_vdim, r_taps;
+    int64_t rq_off, rk_off, rv_off, rg_off, rb_off, ra_off;
+    const float *r_tap_w;            /* [2 r_kv_heads r_dim + r_heads r_vdim, r_taps] */
+    const float *r_a_log, *r_dt_bias, *r_head_norm;
+    const void *r_w_o;               /* [width, r_heads r_vdim] */
+    const float *out_norm_a, *out_norm_b; /* [width] */
+    /* latent attention with a rotated key part (q_rank, kv_rank, dq_norm, dkv_norm, w_uq [heads (dim + rot_dim), q_rank], w_uk, w_uv,
+     * latent_cache rows of kv_rank + rot_dim; qk_freq / rot_pairs / rot_interleaved above) */
+    int64_t rot_dim;
 } atoma_hybrid_layer;
 
 typedef struct atoma_hybrid_model {
@@ -500,7 +679,7 @@ typedef struct atoma_hybrid_batch {
     int64_t long_tokens, long_ctx_sum;
 } atoma_hybrid_batch;
 
-int64_t atoma_hybrid_abi_sizeof(int which); /* 0 layer, 1 model, 2 batch, 3 attention args, 4 gated residual args, 5 latent attention args, 6 expert args, 7 expanded attention args, 8 lanes update args, 9 softmax attention args */
+int64_t atoma_hybrid_abi_sizeof(int which); /* 0 layer, 1 model, 2 batch, 3 attention args, 4 gated residual args, 5 latent attention args, 6 expert args, 7 expanded attention args, 8 lanes update args, 9 softmax attention args, 10 parallel residual args, 11 tap filter args, 12 state scan args, 13 rotary cache args */
 int64_t atoma_hybrid_scratch_bytes(const atoma_hybrid_model *model, int64_t num_tokens, int64_t num_selected);
 void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_hybrid_batch *batch, atoma_stream_t stream);
 

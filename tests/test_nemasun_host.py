@@ -94,7 +94,8 @@ def test_c_structures_have_the_sizes_the_library_was_built_with():
     except Exception:
         pytest.skip("the shared library is not built here")
     mirrors = [_lib.HybridLayer, _lib.HybridModel, _lib.HybridBatch, _lib.SigmoidAttnArgs, _lib.GatedResidualArgs, _lib.LatentAttnArgs,
-               _lib.MoeArgs, _lib.LatentExpandedArgs, _lib.LanesUpdateArgs, _lib.SoftmaxAttnArgs]
+               _lib.MoeArgs, _lib.LatentExpandedArgs, _lib.LanesUpdateArgs, _lib.SoftmaxAttnArgs, _lib.ParallelResidualArgs,
+               _lib.TapFilterArgs, _lib.StateScanArgs, _lib.QkvRopeArgs]
     for i, m in enumerate(mirrors):
         assert L.atoma_hybrid_abi_sizeof(i) == C.sizeof(m), m.__name__
     assert L.atoma_hybrid_abi_sizeof(len(mirrors)) == -1
