@@ -543,7 +543,7 @@ bool parallel_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, co
     // ---- the two sublayers' inputs ----
     const char *hm = s.h, *hf = s.h;
     const int64_t hist = l.taps > 1 ? (l.taps - 1) * W : 0;   // floats of the layer's state row that the input history takes
-    if (l.taps > 1) {
+    if (l.taps > 0) {
         atoma_tap_filter_args f{};
         f.in = s.h;
         f.ld_in = W;

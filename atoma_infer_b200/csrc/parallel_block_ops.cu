@@ -163,7 +163,7 @@ __device__ __forceinline__ float part_sum(float v, float *red, int parts, int pa
 }
 
 template <typename T, int KIND, int RPT>
-__global__ void __launch_bounds__(1024) state_scan_kernel(const atoma_state_scan_args a, int parts) {
+__global__ void __launch_bounds__(512) state_scan_kernel(const atoma_state_scan_args a, int parts) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -525,8 +525,8 @@ bool hyb_state_scan(const atoma_state_scan_args &a, cudaStream_t stream) {
     }
     const int rpt = a.dim <= 64 ? 16 : 32;
     const int parts = static_cast<int>((a.dim + rpt - 1) / rpt);
-    if (parts > 32) {
-        set_status(kErrUnsupported, "atoma_state_scan: a key size of %lld exceeds 1024", static_cast<long long>(a.dim));
+    if (parts > 16) {
+        set_status(kErrUnsupported, "atoma_state_scan: a key size of %lld exceeds 512", static_cast<long long>(a.dim));
         return false;
     }
     const int Dp = parts * rpt;

@@ -238,7 +238,7 @@ class LayerSpec:
     source: Optional[int] = None             # entry of weights["layers"] the run uses; None = its own index
     gla: Optional["GatedLinearAttentionSpec"] = None
     pair: Optional["MixerPairSpec"] = None
-    taps: int = 0                            # parallel blocks: taps of the filters on the sublayers' inputs (<= 1: none)
+    taps: int = 0                            # parallel blocks: taps of the filters on the sublayers' inputs (0: none)
     add_embedding: bool = False              # parallel blocks: the embedding rows are added to the stream before the layer
     pass_vector: Optional[int] = None        # ... and this row of weights["pass_vectors"]
 
@@ -562,7 +562,7 @@ class HybridExecutor:
         L.taps = max(0, int(ls.taps))
         if ls.taps > 16:
             raise AtomaError(f"layer {i}: {ls.taps} taps (at most 16 are supported)")
-        if ls.taps > 1:
+        if ls.taps >= 1:
             L.tap_w1 = small(need("tap_w1", (W, ls.taps))).data_ptr()
         f = ls.mlp
         L.has_mlp = 1 if f is not None else 0
@@ -571,7 +571,7 @@ class HybridExecutor:
                 raise AtomaError(f"layer {i}: unknown activation {f.act!r}")
             L.ff, L.act = f.ff, ACTIVATIONS[f.act]
             L.w_gate_up, L.w_down = big(need("w_gate_up", (2 * f.ff, W))).data_ptr(), big(need("w_down", (W, f.ff))).data_ptr()
-            if ls.taps > 1:
+            if ls.taps >= 1:
                 L.tap_w2 = small(need("tap_w2", (W, ls.taps))).data_ptr()
         if ls.mixer == "gla":
             a = ls.gla
@@ -596,10 +596,7 @@ class HybridExecutor:
             L.mixer = MIXER_LATENT
             L.heads, L.kv_heads, L.dim, L.vdim = a.heads, 1, a.dim, a.vdim
             L.q_rank, L.kv_rank, L.window, L.scale, L.rot_dim = a.q_rank, a.kv_rank, a.window, a.scale, a.rot_dim
-            if a.q_rank % 8:
-                raise AtomaError(f"layer {i}: a query latent of {a.q_rank} entries (a multiple of 8 is needed)")
-            stack("dq", "w_dq", a.q_rank)
-            stack("dkv", "w_dkv", a.kv_rank + a.rot_dim)      # follows the query latent directly: q_rank is a multiple of 8
+            parts.extend([need("w_dq", (a.q_rank, W)), need("w_dkv", (a.kv_rank + a.rot_dim, W))])   # [c_q | c | rotated key part], no padding
             L.proj_cols = sum(p.shape[0] for p in parts)
             L.dq_norm, L.dkv_norm = small(need("dq_norm", (a.q_rank,))).data_ptr(), small(need("dkv_norm", (a.kv_rank,))).data_ptr()
             L.w_uq = big(need("w_uq", (a.heads * (a.dim + a.rot_dim), a.q_rank))).data_ptr()

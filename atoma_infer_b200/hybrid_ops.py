@@ -433,3 +433,126 @@ def moe_expert_rows(h, top_expert, top_weight, w_gate_up, w_down, limit, alpha, 
     _lib.lib().atoma_moe_experts(C.byref(a), C.byref(eo), C.byref(pr), _s())
     _check()
     return eo.value, pr.value, ws
+
+
+# ---- parallel blocks: tap filters, matrix-state recurrences, rotary operators ----
+def parallel_residual_norm(x, dtype, y_a=None, y_b=None, y_ff=None, norm_a=None, norm_b=None, mix_scale=1.0, add_rows=None, add_vec=None,
+                           w_next=None, eps=1e-5, offset=0.0, want_trace=False):
+    """x [T, width] float32 is updated in place; returns (h or None, trace or None)."""
+    from ._lib import ParallelResidualArgs
+    T, W = x.shape
+    h = torch.empty((T, W), dtype=dtype, device=x.device) if w_next is not None else None
+    trace = torch.empty_like(x) if want_trace else None
+    a = ParallelResidualArgs()
+    a.y_a, a.y_b, a.y_ff, a.norm_a, a.norm_b, a.mix_scale = _p(y_a), _p(y_b), _p(y_ff), _p(norm_a), _p(norm_b), mix_scale
+    a.x, a.trace, a.add_rows, a.add_vec, a.w_next, a.h = _p(x), _p(trace), _p(add_rows), _p(add_vec), _p(w_next), _p(h)
+    a.T, a.width, a.eps, a.weight_offset, a.dtype = T, W, eps, offset, _CODES[dtype]
+    _lib.lib().atoma_parallel_residual_norm(C.byref(a), _s())
+    _check()
+    return h, trace
+
+
+def tap_filter(x, w1, w2, history, state_slots, token_seq, query_start, context_lens, residual: bool, act: int = 0):
+    """x [T, channels]; w1 / w2 [channels, taps] float32 (w2 may be None); history [slots, >= (taps - 1) channels] float32 is read
+    and rewritten.  Returns (out1, out2 or None)."""
+    from ._lib import TapFilterArgs
+    T, Cn = x.shape
+    out1 = torch.empty_like(x)
+    out2 = torch.empty_like(x) if w2 is not None else None
+    a = TapFilterArgs()
+    a.in_, a.ld_in, a.w1, a.w2, a.out1, a.out2, a.ld_out = _p(x), x.stride(0), _p(w1), _p(w2), _p(out1), _p(out2), Cn
+    a.history, a.history_stride = _p(history), 0 if history is None else history.stride(0)
+    a.state_slots, a.token_seq, a.query_start, a.context_lens = _p(state_slots), _p(token_seq), _p(query_start), _p(context_lens)
+    a.T, a.B, a.channels, a.taps, a.residual, a.act, a.dtype = T, context_lens.numel(), Cn, w1.shape[1], int(residual), act, _CODES[x.dtype]
+    _lib.lib().atoma_tap_filter(C.byref(a), _s())
+    _check()
+    return out1, out2
+
+
+def _scan_common(a, q, k, v, state, state_slots, query_start, context_lens, H, G, dim, vdim):
+    T = q.shape[0]
+    out = torch.empty((T, H * vdim), dtype=torch.float32, device=q.device)
+    a.q, a.k, a.v, a.ld_q, a.ld_k, a.ld_v = _p(q), _p(k), _p(v), q.stride(0), k.stride(0), v.stride(0)
+    a.state, a.state_stride = _p(state), state.stride(0)
+    a.state_slots, a.query_start, a.context_lens, a.out = _p(state_slots), _p(query_start), _p(context_lens), _p(out)
+    a.T, a.B, a.H, a.G, a.dim, a.vdim, a.dtype = T, context_lens.numel(), H, G, dim, vdim, _CODES[q.dtype]
+    _lib.lib().atoma_state_scan(C.byref(a), _s())
+    _check()
+    return out
+
+
+def gla_scan(q, k, v, z, z_bias, tau, q_scale, state, state_slots, query_start, context_lens, H, dim, vdim):
+    """Gated linear attention over a mixed batch: q, k, z [T, H dim], v [T, H vdim] -> float32 [T, H vdim]; state [slots, H dim vdim]."""
+    from ._lib import StateScanArgs
+    a = StateScanArgs()
+    a.kind, a.z, a.ld_z, a.z_bias, a.tau, a.q_scale = 0, _p(z), z.stride(0), _p(z_bias), tau, q_scale
+    return _scan_common(a, q, k, v, state, state_slots, query_start, context_lens, H, H, dim, vdim)
+
+
+def delta_rule_scan(q, k, v, b_pre, a_pre, a_log, dt_bias, q_scale, state, state_slots, query_start, context_lens, H, G, dim, vdim,
+                    unit_eps=1e-6):
+    """Gated delta rule over a mixed batch: q, k [T, G dim], v [T, H vdim], b_pre, a_pre [T, H] -> float32 [T, H vdim]."""
+    from ._lib import StateScanArgs
+    a = StateScanArgs()
+    a.kind, a.b_pre, a.a_pre, a.ld_b, a.ld_a = 1, _p(b_pre), _p(a_pre), b_pre.stride(0), a_pre.stride(0)
+    a.a_log, a.dt_bias, a.q_scale, a.unit_eps = _p(a_log), _p(dt_bias), q_scale, unit_eps
+    return _scan_common(a, q, k, v, state, state_slots, query_start, context_lens, H, G, dim, vdim)
+
+
+def headnorm_gate(o, weight, gate, H, vdim, eps, dtype):
+    T = o.shape[0]
+    out = torch.empty((T, H * vdim), dtype=dtype, device=o.device)
+    _lib.lib().atoma_headnorm_gate(_p(o), _p(weight), _p(gate), 0 if gate is None else gate.stride(0), _p(out), T, H, vdim, eps,
+                                   _CODES[dtype], _s())
+    _check()
+    return out
+
+
+def qkv_headnorm_rope_cache(proj, q_off, k_off, v_off, q_w, k_w, qk_freq, v_freq, interleaved, positions, slots, k_cache, v_cache, H, G,
+                            dim, vdim, eps):
+    from ._lib import QkvRopeArgs
+    T = proj.shape[0]
+    q = torch.empty((T, H * dim), dtype=proj.dtype, device=proj.device)
+    a = QkvRopeArgs()
+    a.proj, a.ld, a.q_off, a.k_off, a.v_off = _p(proj), proj.stride(0), q_off, k_off, v_off
+    a.q_weight, a.k_weight, a.qk_freq, a.v_freq = _p(q_w), _p(k_w), _p(qk_freq), _p(v_freq)
+    a.rot_pairs, a.v_pairs, a.interleaved = 0 if qk_freq is None else qk_freq.numel(), 0 if v_freq is None else v_freq.numel(), int(interleaved)
+    a.positions, a.slot_mapping, a.q_out, a.k_cache, a.v_cache = _p(positions), _p(slots), _p(q), _p(k_cache), _p(v_cache)
+    a.T, a.H, a.G, a.dim, a.vdim, a.eps, a.dtype = T, H, G, dim, vdim, eps, _CODES[proj.dtype]
+    _lib.lib().atoma_qkv_headnorm_rope_cache(C.byref(a), _s())
+    _check()
+    return q
+
+
+def rotate_heads(x, positions, freq, H, n, interleaved, sign):
+    """In place on x [T, H n]."""
+    _lib.lib().atoma_rotate_heads(_p(x), _p(positions), _p(freq), x.shape[0], H, n, freq.numel(), int(interleaved), sign, _CODES[x.dtype], _s())
+    _check()
+    return x
+
+
+def latent_norm_rope_cache(proj, q_weight, kv_weight, freq, interleaved, positions, slots, cache, q_rank, kv_rank, rot_dim, eps):
+    T = proj.shape[0]
+    cq = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device)
+    _lib.lib().atoma_latent_norm_rope_cache(_p(proj), proj.stride(0), _p(q_weight), _p(kv_weight), _p(freq), 0 if freq is None else freq.numel(),
+                                            int(interleaved), _p(positions), _p(slots), _p(cq), _p(cache), T, q_rank, kv_rank, rot_dim, eps,
+                                            _CODES[proj.dtype], _s())
+    _check()
+    return cq
+
+
+def latent_query_absorb_rope(q, w_uk, freq, interleaved, positions, H, dim, rot_dim, kv_rank):
+    T = q.shape[0]
+    out = torch.empty((T, H, kv_rank + rot_dim), dtype=torch.float32, device=q.device)
+    _lib.lib().atoma_latent_query_absorb_rope(_p(q), _p(w_uk), _p(freq), 0 if freq is None else freq.numel(), int(interleaved), _p(positions),
+                                              _p(out), T, H, dim, rot_dim, kv_rank, _CODES[q.dtype], _s())
+    _check()
+    return out
+
+
+def latent_expand_values(o_lat, w_uv, H, vdim, kv_rank, dtype):
+    T, row = o_lat.shape[0], o_lat.shape[-1]
+    out = torch.empty((T, H * vdim), dtype=dtype, device=o_lat.device)
+    _lib.lib().atoma_latent_expand_values(_p(o_lat), _p(w_uv), _p(out), T, H, vdim, kv_rank, row, _CODES[dtype], _s())
+    _check()
+    return out

@@ -139,13 +139,13 @@ def weights_from_checkpoint(spec: HybridSpec, cfg: dict, ckpt: Dict[str, torch.T
     for i in range(len(cfg["layers"])):
         ls, p = by_layer[i], f"l{i}."
         w = {"norm1": get(p + "norm1", (W,))}
-        if ls.taps > 1:
+        if ls.taps >= 1:
             w["tap_w1"] = get(p + "canon1", (W, ls.taps))
         if ls.mlp is not None:
             F = ls.mlp.ff
             w["w_gate_up"] = torch.cat([get(p + "mlp.gate", (F, W)), get(p + "mlp.up", (F, W))], 0)
             w["w_down"] = get(p + "mlp.down", (W, F))
-            if ls.taps > 1:
+            if ls.taps >= 1:
                 w["tap_w2"] = get(p + "canon2", (W, ls.taps))
         q = p + "mix."
         if ls.gla is not None:

@@ -605,7 +605,7 @@ typedef struct atoma_hybrid_layer {
     /* what precedes the layer: the embedding rows and / or a vector added to the stream (the start of a pass over a looped span) */
     int32_t add_embedding;
     const float *add_vec;            /* [width] or NULL */
-    /* tap filters of the two sublayers' inputs (taps <= 1: none); the layer's state row = [input history | mixer state] */
+    /* tap filters of the two sublayers' inputs (taps <= 0: none); the layer's state row = [input history | mixer state] */
     int64_t taps;
     const float *tap_w1, *tap_w2;    /* [width, taps] */
     float *layer_state;              /* [slots, layer_state_stride] float32 */

@@ -93,6 +93,18 @@ def rotate(x, positions, freqs, layout, sign=1.0):
 
 
 # ---- mixers ----
+def gla_recurrence(q, k, v, alpha):
+    """q, k, alpha [T, H, D], v [T, H, V] -> [T, H, V]:  S <- diag(alpha) S + k v^T;  o = S^T q."""
+    T, H, D = q.shape
+    V = v.shape[-1]
+    o = torch.zeros(T, H, V, dtype=F64)
+    S = torch.zeros(H, D, V, dtype=F64)
+    for t in range(T):
+        S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    return o
+
+
 def gated_linear_attention(h, P, pre, m, eps):
     """Per head a [dim, vdim] state whose rows decay by a data-dependent factor per key channel."""
     T = h.shape[0]
@@ -102,12 +114,7 @@ def gated_linear_attention(h, P, pre, m, eps):
     v = (h @ P[pre + "v"].T).reshape(T, H, V)
     z = (h @ P[pre + "a1"].T) @ P[pre + "a2"].T + P[pre + "a2.b"]
     alpha = (sigma(z) ** (1.0 / tau)).reshape(T, H, D)
-    o = torch.zeros(T, H, V, dtype=F64)
-    S = torch.zeros(H, D, V, dtype=F64)
-    for t in range(T):
-        S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hdv,hd->hv", S, q[t])
-    o = rms_norm(o, P[pre + "norm"], eps).reshape(T, H * V)
+    o = rms_norm(gla_recurrence(q, k, v, alpha), P[pre + "norm"], eps).reshape(T, H * V)
     return (o * silu(h @ P[pre + "g"].T)) @ P[pre + "o"].T
 
 
@@ -120,10 +127,11 @@ def latent_attention(h, P, pre, m, eps, positions):
     freqs = rotary_frequencies(int(rot.get("dims", Rd)), rot.get("base", 10000.0), rot.get("scaling"))
     cq = rms_norm(h @ P[pre + "dq"].T, P[pre + "dq.norm"], eps)
     q = (cq @ P[pre + "uq"].T).reshape(T, H, D + Rd)
-    q_plain, q_rot = q[..., :D], rotate(q[..., D:], positions, freqs, "halves")
+    layout = rot.get("layout", "halves")
+    q_plain, q_rot = q[..., :D], rotate(q[..., D:], positions, freqs, layout)
     dkv = h @ P[pre + "dkv"].T
     c = rms_norm(dkv[:, :R], P[pre + "dkv.norm"], eps)
-    k_rot = rotate(dkv[:, R:], positions, freqs, "halves")
+    k_rot = rotate(dkv[:, R:], positions, freqs, layout)
     k_plain = (c @ P[pre + "uk"].T).reshape(T, H, D)
     v = (c @ P[pre + "uv"].T).reshape(T, H, V)
     out = torch.zeros(T, H, V, dtype=F64)
@@ -139,9 +147,9 @@ def sigmoid_attention_rotated_values(h, P, pre, m, eps, positions, layout="inter
     when stored and a head's sum is turned back by the query's position."""
     T = h.shape[0]
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    rot = m["rot"]
-    f_qk = rotary_frequencies(int(rot["dims"]), rot["base"], rot.get("scaling"))
-    f_v = rotary_frequencies(V, rot["base"], None)
+    rot = m.get("rot")
+    f_qk = rotary_frequencies(int(rot["dims"]), rot["base"], rot.get("scaling")) if rot else torch.zeros(0, dtype=F64)
+    f_v = rotary_frequencies(V, rot["base"], None) if rot else torch.zeros(0, dtype=F64)
     q = rms_norm((h @ P[pre + "q"].T).reshape(T, H, D), P[pre + "q.norm"], eps)
     k = rms_norm((h @ P[pre + "k"].T).reshape(T, G, D), P[pre + "k.norm"], eps)
     q, k = rotate(q, positions, f_qk, layout), rotate(k, positions, f_qk, layout)
@@ -156,19 +164,15 @@ def sigmoid_attention_rotated_values(h, P, pre, m, eps, positions, layout="inter
     return out.reshape(T, H * V) @ P[pre + "o"].T
 
 
-def gated_delta_rule(h, P, pre, m, eps):
-    """Per head a [dim, vdim] state: decay, then replace what the key reads by a blend with the new value, then read."""
-    T = h.shape[0]
-    H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+def unit_length(x, eps=1e-6):
+    return x / torch.sqrt((x * x).sum(-1, keepdim=True) + eps)
 
-    def short(name, n):
-        return silu(causal_taps(h @ P[pre + name].T, P[pre + name + ".conv"])).reshape(T, n, -1)
 
-    q, k, v = short("q", G), short("k", G), short("v", H)
-    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
-    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    beta = sigma(h @ P[pre + "b"].T)
-    decay = torch.exp(-torch.exp(P[pre + "A_log"]) * softplus(h @ P[pre + "a"].T + P[pre + "dt_bias"]))
+def delta_recurrence(q, k, v, beta, decay):
+    """q, k [T, G, D] (head h reads group h // (H / G)), v [T, H, V], beta, decay [T, H] -> [T, H, V]:
+    S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q (the read-out sees the token's own write)."""
+    T, G, D = q.shape
+    H, V = v.shape[1], v.shape[2]
     o = torch.zeros(T, H, V, dtype=F64)
     S = torch.zeros(H, D, V, dtype=F64)
     for t in range(T):
@@ -178,7 +182,21 @@ def gated_delta_rule(h, P, pre, m, eps):
             u = beta[t, hd] * (v[t, hd] - S[hd].T @ k[t, g])
             S[hd] = S[hd] + torch.outer(k[t, g], u)
             o[t, hd] = S[hd].T @ q[t, g]
-    o = rms_norm(o, P[pre + "norm"], eps).reshape(T, H * V)
+    return o
+
+
+def gated_delta_rule(h, P, pre, m, eps):
+    """Per head a [dim, vdim] state: decay, then replace what the key reads by a blend with the new value, then read."""
+    T = h.shape[0]
+    H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+
+    def short(name, n):
+        return silu(causal_taps(h @ P[pre + name].T, P[pre + name + ".conv"])).reshape(T, n, -1)
+
+    q, k, v = unit_length(short("q", G)) * D ** -0.5, unit_length(short("k", G)), short("v", H)
+    beta = sigma(h @ P[pre + "b"].T)
+    decay = torch.exp(-torch.exp(P[pre + "A_log"]) * softplus(h @ P[pre + "a"].T + P[pre + "dt_bias"]))
+    o = rms_norm(delta_recurrence(q, k, v, beta, decay), P[pre + "norm"], eps).reshape(T, H * V)
     return (o * silu(h @ P[pre + "g"].T)) @ P[pre + "o"].T
 
 
@@ -205,7 +223,7 @@ def layer(x, P, i, lc, eps, positions):
     elif kind == "latent_attention":
         y = latent_attention(hm, P, p + "mix.", m, eps, positions)
     elif kind == "parallel":
-        y = paired_mixer(hm, P, p + "mix.", m, eps, positions)
+        y = paired_mixer(hm, P, p + "mix.", m, eps, positions, (m["left"].get("rot") or {}).get("layout", "interleaved"))
     else:
         raise ValueError(kind)
     if lc.get("mlp") is not None:
@@ -243,3 +261,81 @@ def forward(cfg, P, tokens):
         trace.append(x)
     logits = rms_norm(x, P["final.norm"], eps) @ P["head"].T
     return logits, torch.stack(trace)
+
+
+# ---- random small models for the tests ----
+def random_config(width=48, vocab=61, taps=3, kinds=("gla", "latent_attention", "parallel", "gla"), loop=(0, 2, 2), ff=40, mlps=None, eps=1e-5,
+                  gla=None, latent=None, left=None, right=None):
+    """A configuration in the checkpoint's format.  `mlps`: per layer True / False (no feed-forward); mixer sizes by keyword."""
+    g_ = dict(heads=2, dim=16, vdim=24, tau=8.0)
+    g_.update(gla or {})
+    l_ = dict(heads=3, dim=16, rot_dim=8, vdim=16, q_rank=24, kv_rank=32, scale=0.2, rot=dict(base=5000.0, dims=8))
+    l_.update(latent or {})
+    a_ = dict(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.25, rot=dict(base=20000.0, dims=8, scaling=dict(factor=3.0, low=1.0, high=3.0, original=64)))
+    a_.update(left or {})
+    r_ = dict(heads=4, kv_heads=2, dim=16, vdim=24, conv=3)
+    r_.update(right or {})
+    layers = []
+    for i, kind in enumerate(kinds):
+        mixer = {"gla": g_, "latent_attention": l_, "parallel": dict(left=a_, right=r_)}[kind]
+        has = True if mlps is None else mlps[i]
+        layers.append(dict(type=kind, mixer=json_copy(mixer), mlp=dict(kind="dense", ff=ff) if has else None))
+    cfg = dict(architecture="Surinex", vocab=vocab, width=width, norm=dict(eps=eps), canon=dict(taps=taps), layers=layers)
+    if loop is not None:
+        cfg["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])
+    return cfg
+
+
+def json_copy(x):
+    import json
+    return json.loads(json.dumps(x))
+
+
+def random_weights(cfg, g, decay_rank=5):
+    """float32 tensors under the checkpoint's names, already rounded to bfloat16 values (so that a bfloat16 file holds them exactly)."""
+    W, P = cfg["width"], {}
+
+    def rnd(*shape, scale=1.0, shift=0.0):
+        return ((torch.randn(*shape, generator=g) * scale + shift).to(torch.bfloat16)).float()
+
+    def lin(out, inp, gain=1.0):
+        return rnd(out, inp, scale=gain * inp ** -0.5)
+
+    P["embed"], P["head"], P["final.norm"] = rnd(cfg["vocab"], W), lin(cfg["vocab"], W), rnd(W, scale=0.1, shift=1.0)
+    if cfg.get("loop"):
+        P["loop.step"] = rnd(cfg["loop"]["times"], W, scale=0.3)
+    taps = cfg["canon"]["taps"]
+    for i, l in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", l["mixer"]
+        P[p + "norm1"] = rnd(W, scale=0.1, shift=1.0)
+        P[p + "canon1"] = rnd(W, taps, scale=0.3)
+        if l["mlp"] is not None:
+            F = l["mlp"]["ff"]
+            P[p + "canon2"] = rnd(W, taps, scale=0.3)
+            P[p + "mlp.gate"], P[p + "mlp.up"], P[p + "mlp.down"] = lin(F, W), lin(F, W), lin(W, F)
+        q = p + "mix."
+        if l["type"] == "gla":
+            H, D, V = m["heads"], m["dim"], m["vdim"]
+            P[q + "q"], P[q + "k"], P[q + "v"], P[q + "g"] = lin(H * D, W), lin(H * D, W), lin(H * V, W), lin(H * V, W)
+            P[q + "a1"], P[q + "a2"], P[q + "a2.b"] = lin(decay_rank, W), lin(H * D, decay_rank, 2.0), rnd(H * D, scale=1.0, shift=2.0)
+            P[q + "norm"], P[q + "o"] = rnd(V, scale=0.1, shift=1.0), lin(W, H * V)
+        elif l["type"] == "latent_attention":
+            H, D, Rd, V, Rq, Rk = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
+            P[q + "dq"], P[q + "dq.norm"], P[q + "uq"] = lin(Rq, W), rnd(Rq, scale=0.1, shift=1.0), lin(H * (D + Rd), Rq, 2.0)
+            P[q + "dkv"], P[q + "dkv.norm"] = lin(Rk + Rd, W, 2.0), rnd(Rk, scale=0.1, shift=1.0)
+            P[q + "uk"], P[q + "uv"], P[q + "o"] = lin(H * D, Rk, 2.0), lin(H * V, Rk), lin(W, H * V)
+        else:
+            a, d = m["left"], m["right"]
+            H, G, D, V = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            x = q + "left."
+            P[x + "q"], P[x + "k"], P[x + "v"] = lin(H * D, W), lin(G * D, W), lin(G * V, W)
+            P[x + "q.norm"], P[x + "k.norm"] = rnd(D, scale=0.2, shift=1.5), rnd(D, scale=0.2, shift=1.5)
+            P[x + "pb"], P[x + "o"], P[x + "out"] = rnd(H, scale=0.5, shift=-2.0), lin(W, H * V), rnd(W, scale=0.1, shift=1.0)
+            H, G, D, V, K = d["heads"], d["kv_heads"], d["dim"], d["vdim"], d["conv"]
+            x = q + "right."
+            P[x + "q"], P[x + "k"], P[x + "v"], P[x + "g"] = lin(G * D, W), lin(G * D, W), lin(H * V, W), lin(H * V, W)
+            P[x + "q.conv"], P[x + "k.conv"], P[x + "v.conv"] = rnd(G * D, K, scale=0.5), rnd(G * D, K, scale=0.5), rnd(H * V, K, scale=0.5)
+            P[x + "b"], P[x + "a"] = lin(H, W), lin(H, W)
+            P[x + "A_log"], P[x + "dt_bias"] = rnd(H, scale=0.5, shift=-1.0), rnd(H, scale=0.5)
+            P[x + "norm"], P[x + "o"], P[x + "out"] = rnd(V, scale=0.1, shift=1.0), lin(W, H * V), rnd(W, scale=0.1, shift=1.0)
+    return P
