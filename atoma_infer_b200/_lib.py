@@ -289,7 +289,7 @@ class LatentAttnArgs(C.Structure):
     _fields_ = ([(n, C.c_void_p) for n in ("q_lat", "latent_cache", "out", "positions", "token_seq", "query_start", "block_tables", "sink")] +
                 [(n, C.c_int64) for n in ("T", "B", "max_blocks", "H", "R", "block_size", "window")] +
                 [("scale", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32), ("max_seq_len", C.c_int32),
-                 ("skip_min_q", C.c_int32)])
+                 ("skip_min_q", C.c_int32), ("out_cols", C.c_int64)])
 
 
 class LatentExpandedArgs(C.Structure):

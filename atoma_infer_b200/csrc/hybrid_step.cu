@@ -641,6 +641,7 @@ bool parallel_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, co
         a.dtype = dt;
         a.max_query_len = b.max_query_len;
         a.max_seq_len = b.max_seq_len;
+        a.out_cols = l.kv_rank;            // the rotated tail of a cached row takes part in the scores only
         if (!hyb_latent_attention(a, stream)) return false;
         if (!hyb_latent_expand_values(s.olat, l.w_uv, s.act, T, H, l.vdim, l.kv_rank, row, dt, stream)) return false;
         if (!hyb_linear(s.act, l.w_o, s.y, T, W, H * l.vdim, dt, stream)) return false;

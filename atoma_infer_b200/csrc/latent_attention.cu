@@ -342,7 +342,8 @@ __global__ void __launch_bounds__(32 * NW) latent_attn_tc_kernel(const atoma_lat
         }
         cp_async_commit();
     };
-    const int NT = R / (8 * NW);               // n8 tiles of this warp's output columns (even)
+    const int Rv = a.out_cols > 0 ? static_cast<int>(a.out_cols) : R;   // columns of the weighted sum that anyone reads
+    const int NT = Rv / (8 * NW);              // n8 tiles of this warp's output columns (even)
     float acc[MT][kTcMaxNT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -352,7 +353,7 @@ __global__ void __launch_bounds__(32 * NW) latent_attn_tc_kernel(const atoma_lat
             for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
     const int g = lane >> 2, t4 = lane & 3;
     const int kq = warp & 3, key0 = NW == 8 ? (warp >> 2) * 16 : 0;
-    const int col0 = warp * (R / NW);
+    const int col0 = warp * (Rv / NW);
     if (k_lo < k_hi) stage(k_lo, 0);
     int it = 0;
     for (int j0 = k_lo; j0 < k_hi; j0 += kTcKeys, ++it) {
@@ -642,12 +643,14 @@ bool hyb_head_project(const void *in, const void *w, void *out, int64_t T, int64
     return hyb_head_project_ld(in, H * R, R, w, out, H * n, n, T, H, n, R, 0, dtype, stream);
 }
 
-// The tensor-core kernel takes bfloat16 caches whose latent size is a multiple of 64 up to 256 (four warps) or a multiple of
-// 128 up to 512 (eight warps): 16-byte rows for cp.async, whole ldmatrix tiles per warp, at most 8 accumulator tiles per
-// warp and row tile.  Everything else runs the general kernel.
+// The tensor-core kernel takes bfloat16 caches whose rows are a multiple of 64 entries (16-byte rows for cp.async, whole ldmatrix
+// tiles per quarter of the row in the score product) and whose summed columns (all of the row, or its first out_cols) are a
+// multiple of 64 up to 256 (four warps) or a multiple of 128 up to 512 (eight warps): at most 8 accumulator tiles per warp and row
+// tile.  Rows of up to 576 entries fit shared memory.  Everything else runs the general kernel.
 bool hyb_latent_attention_tc(const atoma_latent_attn_args &a, cudaStream_t stream, bool *taken) {
     *taken = false;
-    const bool four = a.R % 64 == 0 && a.R <= 256, eight = a.R % 128 == 0 && a.R > 256 && a.R <= 512;
+    const int64_t rv = a.out_cols > 0 ? a.out_cols : a.R;
+    const bool four = a.R % 64 == 0 && a.R <= 256 && rv % 64 == 0, eight = a.R % 64 == 0 && a.R > 256 && a.R <= 576 && rv % 128 == 0 && rv <= 512;
     if (a.dtype != ATOMA_DTYPE_BF16 || (g_hybrid_debug & 2) || !(four || eight) || !a.query_start || a.max_query_len <= 0 ||
         (reinterpret_cast<uintptr_t>(a.latent_cache) & 15) || (reinterpret_cast<uintptr_t>(a.q_lat) & 15) ||
         current_device_info().cc_major < 8)
@@ -699,7 +702,7 @@ bool hyb_latent_attention(const atoma_latent_attn_args &a, cudaStream_t stream) 
     if (a.T <= 0) return true;
     if (!hybrid::known_dtype(a.dtype, "atoma_latent_attention_paged")) return false;
     if (!a.q_lat || !a.latent_cache || !a.out || !a.positions || !a.token_seq || !a.block_tables || a.H <= 0 || a.R <= 0 ||
-        a.block_size <= 0 || a.max_blocks <= 0) {
+        a.block_size <= 0 || a.max_blocks <= 0 || a.out_cols < 0 || a.out_cols > a.R) {
         set_status(kErrInvalidArg, "atoma_latent_attention_paged: null argument or empty shape");
         return false;
     }

@@ -28,8 +28,6 @@ namespace {
 using namespace hybrid;
 
 constexpr int kMaxTaps = 16;
-constexpr int kScanCols = 32;     // columns of the state per CTA
-constexpr int kScanChunk = 8;     // tokens staged in shared memory at a time
 
 // ---------------------------------------------------------------------------------------------
 // residual update of a parallel block + what precedes the next layer + its input norm
@@ -151,79 +149,60 @@ __global__ void __launch_bounds__(256) tap_history_kernel(const atoma_tap_filter
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// Sum of one value per part for every column; parts write, one barrier, every thread adds the parts in index order.
-template <int RPT>
-__device__ __forceinline__ float part_sum(float v, float *red, int parts, int part, int col) {
-    if (parts == 1) return v;
-    red[part * kScanCols + col] = v;
-    __syncthreads();
-    float s = 0.f;
-    for (int p = 0; p < parts; ++p) s += red[p * kScanCols + col];
-    return s;
+// One CTA = kScanWarps compute warps + kScanWarps staging warps for 32 * kScanWarps / PW columns of one head of one sequence.
+// A compute warp owns 32 / PW columns; the dim rows of a column are spread over PW lanes (RPT registers each), so the sums over
+// the rows are PW-lane shuffles in a fixed order and the token loop has no CTA-wide barrier.  While the compute warps walk through
+// one chunk of staged tokens, the staging warps load the next one (number-format conversion, the decays' exponentials, the unit
+// norms of q and k) into the other buffer; one barrier per chunk.
+// Staged row of a token: element i of q / k / decay at (i / RPT) * (RPT + 4) + i % RPT — a lane's RPT values are contiguous and
+// 16-byte aligned (float4 loads), and the PW lanes of a column read distinct banks.
+constexpr int kScanWarps = 4;
+
+template <int PW>
+__device__ __forceinline__ float parts_sum(float v) {
+#pragma unroll
+    for (int o = 32 / PW; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
 }
 
-template <typename T, int KIND, int RPT>
-__global__ void __launch_bounds__(512) state_scan_kernel(const atoma_state_scan_args a, int parts) {
-    extern __shared__ float sm[];
+template <typename T, int KIND, int RPT, int PW>
+__global__ void __launch_bounds__(64 * kScanWarps) state_scan_kernel(const atoma_state_scan_args a, int chunk) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int CW = 32 / PW, COLS = CW * kScanWarps, DS = PW * (RPT + 4);
     pdl_launch_dependents();
     pdl_wait();
-    const int col = threadIdx.x, part = threadIdx.y;
-    const int tid = part * kScanCols + col, nthr = parts * kScanCols;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y, b = blockIdx.z;
     const int D = static_cast<int>(a.dim), V = static_cast<int>(a.vdim), H = static_cast<int>(a.H);
-    const int Dp = parts * RPT;                              // padded rows: what lies beyond dim stays zero
-    const int j = blockIdx.x * kScanCols + col;
     const int q0 = a.query_start[b], n = a.query_start[b + 1] - q0;
     if (n <= 0) return;
-    float *q_s = sm;                                         // [chunk][Dp]
-    float *k_s = q_s + kScanChunk * Dp;
-    float *a_s = k_s + kScanChunk * Dp;                      // kind 0: decay per key channel; kind 1: [chunk][2] = beta, decay
-    float *v_s = a_s + (KIND == 0 ? kScanChunk * Dp : kScanChunk * 2);   // [chunk][32]
-    float *red = v_s + kScanChunk * kScanCols;               // [2][parts][32]
+    const int per_tok = (KIND == 0 ? 3 : 2) * DS + COLS + 4;     // q, k, (decay per channel), v of the CTA's columns, beta and decay
+    float *bufs[2] = {sm, sm + chunk * per_tok};
+    for (int i = threadIdx.x; i < 2 * chunk * per_tok; i += blockDim.x) sm[i] = 0.f;   // what lies beyond dim stays zero
     const int kvh = KIND == 1 ? h / (H / static_cast<int>(a.G)) : h;
-    float *S_g = a.state + static_cast<int64_t>(a.state_slots[b]) * a.state_stride + static_cast<int64_t>(h) * D * V;
-    float S[RPT];
-    const bool fresh = a.context_lens[b] == 0;
-#pragma unroll
-    for (int r = 0; r < RPT; ++r) {
-        const int i = part * RPT + r;
-        S[r] = (!fresh && i < D && j < V) ? S_g[static_cast<int64_t>(i) * V + j] : 0.f;
-    }
     const T *qp = static_cast<const T *>(a.q), *kp = static_cast<const T *>(a.k), *vp = static_cast<const T *>(a.v);
-    int flip = 0;
-    for (int t0 = 0; t0 < n; t0 += kScanChunk) {
-        const int nt = min(kScanChunk, n - t0);
-        __syncthreads();                                     // the previous chunk has been consumed
-        for (int idx = tid; idx < nt * Dp; idx += nthr) {
-            const int tk = idx / Dp, i = idx % Dp;
+    const int jb = blockIdx.x * COLS;
+    const bool loader = warp >= kScanWarps;
+    // ---- staging (all warps for the first chunk, the staging warps afterwards) ----
+    auto stage = [&](int t0, float *buf, int w, int nw) {
+        const int nt = min(chunk, n - t0);
+        for (int tk = w; tk < nt; tk += nw) {
             const int64_t t = q0 + t0 + tk;
-            float qv = 0.f, kv = 0.f, av = 0.f;
-            if (i < D) {
-                qv = to_f(qp[t * a.ld_q + kvh * D + i]);
-                kv = to_f(kp[t * a.ld_k + kvh * D + i]);
-                if (KIND == 0) {
-                    qv *= a.q_scale;
+            float *row = buf + tk * per_tok;
+            if (KIND == 0) {
+                for (int i = lane; i < D; i += 32) {
+                    const int o = (i / RPT) * (RPT + 4) + i % RPT;
+                    row[o] = to_f(qp[t * a.ld_q + h * D + i]) * a.q_scale;
+                    row[DS + o] = to_f(kp[t * a.ld_k + h * D + i]);
                     const float z = to_f(static_cast<const T *>(a.z)[t * a.ld_z + h * D + i]) + a.z_bias[h * D + i];
-                    av = expf(log_sigmoid(z) / a.tau);
+                    row[2 * DS + o] = expf(log_sigmoid(z) / a.tau);
                 }
-            }
-            q_s[idx] = qv;
-            k_s[idx] = kv;
-            if (KIND == 0) a_s[idx] = av;
-        }
-        for (int idx = tid; idx < nt * kScanCols; idx += nthr) {
-            const int tk = idx / kScanCols, cc = idx % kScanCols;
-            const int jj = blockIdx.x * kScanCols + cc;
-            v_s[idx] = jj < V ? to_f(vp[static_cast<int64_t>(q0 + t0 + tk) * a.ld_v + h * V + jj]) : 0.f;
-        }
-        if (KIND == 1) {
-            __syncthreads();
-            // unit length per head: one warp per staged token, lanes over the channels in a fixed order
-            for (int tk = part; tk < nt; tk += parts) {
+            } else {
                 float sq = 0.f, sk = 0.f;
-                for (int i = col; i < D; i += kScanCols) {
-                    sq = fmaf(q_s[tk * Dp + i], q_s[tk * Dp + i], sq);
-                    sk = fmaf(k_s[tk * Dp + i], k_s[tk * Dp + i], sk);
+                for (int i = lane; i < D; i += 32) {
+                    const float qv = to_f(qp[t * a.ld_q + kvh * D + i]), kv = to_f(kp[t * a.ld_k + kvh * D + i]);
+                    sq = fmaf(qv, qv, sq);
+                    sk = fmaf(kv, kv, sk);
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) {
@@ -231,59 +210,108 @@ __global__ void __launch_bounds__(512) state_scan_kernel(const atoma_state_scan_
                     sk += __shfl_xor_sync(0xffffffffu, sk, o);
                 }
                 const float iq = a.q_scale / sqrtf(sq + a.unit_eps), ik = 1.0f / sqrtf(sk + a.unit_eps);
-                for (int i = col; i < D; i += kScanCols) {
-                    q_s[tk * Dp + i] *= iq;
-                    k_s[tk * Dp + i] *= ik;
+                for (int i = lane; i < D; i += 32) {
+                    const int o = (i / RPT) * (RPT + 4) + i % RPT;
+                    row[o] = to_f(qp[t * a.ld_q + kvh * D + i]) * iq;
+                    row[DS + o] = to_f(kp[t * a.ld_k + kvh * D + i]) * ik;
                 }
-                if (col == 0) {
-                    const int64_t t = q0 + t0 + tk;
+                if (lane == 0) {
                     const float bp = to_f(static_cast<const T *>(a.b_pre)[t * a.ld_b + h]);
                     const float ap = to_f(static_cast<const T *>(a.a_pre)[t * a.ld_a + h]) + a.dt_bias[h];
-                    a_s[tk * 2] = sigmoidf_(bp);
-                    a_s[tk * 2 + 1] = expf(-expf(a.a_log[h]) * softplusf_(ap));
+                    row[per_tok - 4] = sigmoidf_(bp);
+                    row[per_tok - 3] = expf(-expf(a.a_log[h]) * softplusf_(ap));
                 }
+            }
+            float *vrow = row + (KIND == 0 ? 3 : 2) * DS;
+            for (int c = lane; c < COLS; c += 32) vrow[c] = jb + c < V ? to_f(vp[t * a.ld_v + h * V + jb + c]) : 0.f;
+        }
+    };
+    // ---- the state of this lane: rows part * RPT + r of column j ----
+    const int part = lane / CW, j = jb + (warp % kScanWarps) * CW + lane % CW;
+    float *S_g = a.state + static_cast<int64_t>(a.state_slots[b]) * a.state_stride + static_cast<int64_t>(h) * D * V;
+    float S[RPT];
+    const bool fresh = a.context_lens[b] == 0;
+    if (!loader) {
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) {
+            const int i = part * RPT + r;
+            S[r] = (!fresh && i < D && j < V) ? S_g[static_cast<int64_t>(i) * V + j] : 0.f;
+        }
+    }
+    __syncthreads();                                         // the zero fill is done
+    stage(0, bufs[0], warp, 2 * kScanWarps);
+    __syncthreads();
+    int it = 0;
+    for (int t0 = 0; t0 < n; t0 += chunk, ++it) {
+        float *buf = bufs[it & 1];
+        if (loader) {
+            if (t0 + chunk < n) stage(t0 + chunk, bufs[(it + 1) & 1], warp - kScanWarps, kScanWarps);
+        } else {
+            const int nt = min(chunk, n - t0);
+            for (int tk = 0; tk < nt; ++tk) {
+                const float *row = buf + tk * per_tok;
+                const float4 *qr = reinterpret_cast<const float4 *>(row + part * (RPT + 4));
+                const float4 *kr = reinterpret_cast<const float4 *>(row + DS + part * (RPT + 4));
+                const float vj = row[(KIND == 0 ? 3 : 2) * DS + (warp % kScanWarps) * CW + lane % CW];
+                float o;
+                if (KIND == 0) {
+                    const float4 *ar = reinterpret_cast<const float4 *>(row + 2 * DS + part * (RPT + 4));
+                    float acc = 0.f;
+#pragma unroll
+                    for (int r4 = 0; r4 < RPT / 4; ++r4) {
+                        const float4 a4 = ar[r4], k4 = kr[r4], q4 = qr[r4];
+                        S[4 * r4] = fmaf(a4.x, S[4 * r4], k4.x * vj);
+                        acc = fmaf(S[4 * r4], q4.x, acc);
+                        S[4 * r4 + 1] = fmaf(a4.y, S[4 * r4 + 1], k4.y * vj);
+                        acc = fmaf(S[4 * r4 + 1], q4.y, acc);
+                        S[4 * r4 + 2] = fmaf(a4.z, S[4 * r4 + 2], k4.z * vj);
+                        acc = fmaf(S[4 * r4 + 2], q4.z, acc);
+                        S[4 * r4 + 3] = fmaf(a4.w, S[4 * r4 + 3], k4.w * vj);
+                        acc = fmaf(S[4 * r4 + 3], q4.w, acc);
+                    }
+                    o = parts_sum<PW>(acc);
+                } else {
+                    const float beta = row[per_tok - 4], g = row[per_tok - 3];
+                    float acc = 0.f;
+#pragma unroll
+                    for (int r4 = 0; r4 < RPT / 4; ++r4) {
+                        const float4 k4 = kr[r4];
+                        S[4 * r4] *= g;
+                        acc = fmaf(S[4 * r4], k4.x, acc);
+                        S[4 * r4 + 1] *= g;
+                        acc = fmaf(S[4 * r4 + 1], k4.y, acc);
+                        S[4 * r4 + 2] *= g;
+                        acc = fmaf(S[4 * r4 + 2], k4.z, acc);
+                        S[4 * r4 + 3] *= g;
+                        acc = fmaf(S[4 * r4 + 3], k4.w, acc);
+                    }
+                    const float u = beta * (vj - parts_sum<PW>(acc));
+                    acc = 0.f;
+#pragma unroll
+                    for (int r4 = 0; r4 < RPT / 4; ++r4) {
+                        const float4 k4 = kr[r4], q4 = qr[r4];
+                        S[4 * r4] = fmaf(k4.x, u, S[4 * r4]);
+                        acc = fmaf(S[4 * r4], q4.x, acc);
+                        S[4 * r4 + 1] = fmaf(k4.y, u, S[4 * r4 + 1]);
+                        acc = fmaf(S[4 * r4 + 1], q4.y, acc);
+                        S[4 * r4 + 2] = fmaf(k4.z, u, S[4 * r4 + 2]);
+                        acc = fmaf(S[4 * r4 + 2], q4.z, acc);
+                        S[4 * r4 + 3] = fmaf(k4.w, u, S[4 * r4 + 3]);
+                        acc = fmaf(S[4 * r4 + 3], q4.w, acc);
+                    }
+                    o = parts_sum<PW>(acc);
+                }
+                if (part == 0 && j < V) a.out[static_cast<int64_t>(q0 + t0 + tk) * H * V + h * V + j] = o;
             }
         }
         __syncthreads();
-        for (int tk = 0; tk < nt; ++tk) {
-            const float *qr = q_s + tk * Dp + part * RPT, *kr = k_s + tk * Dp + part * RPT;
-            const float vj = v_s[tk * kScanCols + col];
-            float o;
-            if (KIND == 0) {
-                const float *ar = a_s + tk * Dp + part * RPT;
-                float acc = 0.f;
-#pragma unroll
-                for (int r = 0; r < RPT; ++r) {
-                    S[r] = fmaf(ar[r], S[r], kr[r] * vj);
-                    acc = fmaf(S[r], qr[r], acc);
-                }
-                o = part_sum<RPT>(acc, red + flip * parts * kScanCols, parts, part, col);
-                flip ^= 1;
-            } else {
-                const float beta = a_s[tk * 2], g = a_s[tk * 2 + 1];
-                float acc = 0.f;
-#pragma unroll
-                for (int r = 0; r < RPT; ++r) {
-                    S[r] *= g;
-                    acc = fmaf(S[r], kr[r], acc);
-                }
-                const float read = part_sum<RPT>(acc, red, parts, part, col);
-                const float u = beta * (vj - read);
-                acc = 0.f;
-#pragma unroll
-                for (int r = 0; r < RPT; ++r) {
-                    S[r] = fmaf(kr[r], u, S[r]);
-                    acc = fmaf(S[r], qr[r], acc);
-                }
-                o = part_sum<RPT>(acc, red + parts * kScanCols, parts, part, col);
-            }
-            if (part == 0 && j < V) a.out[static_cast<int64_t>(q0 + t0 + tk) * H * V + h * V + j] = o;
-        }
     }
+    if (!loader) {
 #pragma unroll
-    for (int r = 0; r < RPT; ++r) {
-        const int i = part * RPT + r;
-        if (i < D && j < V) S_g[static_cast<int64_t>(i) * V + j] = S[r];
+        for (int r = 0; r < RPT; ++r) {
+            const int i = part * RPT + r;
+            if (i < D && j < V) S_g[static_cast<int64_t>(i) * V + j] = S[r];
+        }
     }
 }
 
@@ -523,33 +551,43 @@ bool hyb_state_scan(const atoma_state_scan_args &a, cudaStream_t stream) {
         set_status(kErrInvalidArg, "atoma_state_scan: null argument, unknown kind %d, or a state row shorter than heads * dim * vdim", a.kind);
         return false;
     }
+    // rows of a column per lane (RPT) and lanes per column (PW): dim <= RPT * PW
     const int rpt = a.dim <= 64 ? 16 : 32;
-    const int parts = static_cast<int>((a.dim + rpt - 1) / rpt);
-    if (parts > 16) {
+    const int pw = a.dim <= 128 ? 4 : (a.dim <= 256 ? 8 : 16);
+    if (a.dim > 512) {
         set_status(kErrUnsupported, "atoma_state_scan: a key size of %lld exceeds 512", static_cast<long long>(a.dim));
         return false;
     }
-    const int Dp = parts * rpt;
-    const size_t smem = static_cast<size_t>(2 * kScanChunk * Dp + (gla ? kScanChunk * Dp : kScanChunk * 2) + kScanChunk * kScanCols +
-                                            2 * parts * kScanCols) * 4;
-    const dim3 grid(static_cast<unsigned>((a.vdim + kScanCols - 1) / kScanCols), static_cast<unsigned>(a.H), static_cast<unsigned>(a.B));
-    const dim3 block(kScanCols, static_cast<unsigned>(parts));
+    const int cols = 32 / pw * kScanWarps;
+    const int per_tok = (gla ? 3 : 2) * pw * (rpt + 4) + cols + 4;
+    int64_t longest = a.T;                                   // a bound of the longest portion: T tokens over B sequences, each has one at least
+    longest = std::max<int64_t>(1, a.T - (a.B - 1));
+    const int chunk = static_cast<int>(std::min<int64_t>(32, longest));
+    const size_t smem = static_cast<size_t>(2 * chunk * per_tok) * 4;
+    const dim3 grid(static_cast<unsigned>((a.vdim + cols - 1) / cols), static_cast<unsigned>(a.H), static_cast<unsigned>(a.B));
+    const dim3 block(64 * kScanWarps);
     cudaError_t e;
-#define SCAN(TT, KIND, RPT)                                                                                                  \
-    do {                                                                                                                      \
-        if (smem > 48 * 1024) cudaFuncSetAttribute(state_scan_kernel<TT, KIND, RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
-        e = launch_ex(state_scan_kernel<TT, KIND, RPT>, grid, block, smem, stream, a, parts);                                 \
+#define SCAN(TT, KIND, RPT, PW)                                                                                                    \
+    do {                                                                                                                            \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(state_scan_kernel<TT, KIND, RPT, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+        e = launch_ex(state_scan_kernel<TT, KIND, RPT, PW>, grid, block, smem, stream, a, chunk);                                   \
+    } while (0)
+#define SCAN_K(TT, KIND)                                \
+    do {                                                \
+        if (rpt == 16) SCAN(TT, KIND, 16, 4);           \
+        else if (pw == 4) SCAN(TT, KIND, 32, 4);        \
+        else if (pw == 8) SCAN(TT, KIND, 32, 8);        \
+        else SCAN(TT, KIND, 32, 16);                    \
     } while (0)
 #define SCAN_T(TT)                                      \
     do {                                                \
-        if (gla && rpt == 16) SCAN(TT, 0, 16);          \
-        else if (gla) SCAN(TT, 0, 32);                  \
-        else if (rpt == 16) SCAN(TT, 1, 16);            \
-        else SCAN(TT, 1, 32);                           \
+        if (gla) SCAN_K(TT, 0);                         \
+        else SCAN_K(TT, 1);                             \
     } while (0)
     if (a.dtype == ATOMA_DTYPE_BF16) SCAN_T(__nv_bfloat16);
     else SCAN_T(float);
 #undef SCAN_T
+#undef SCAN_K
 #undef SCAN
     return hybrid::launched(e, "state_scan_kernel");
 }

@@ -209,7 +209,7 @@ def head_project(x, w, H, n, R, absorb: bool):
 
 
 def latent_attention_paged(q_lat, cache, positions, token_seq, block_tables, sink, H, R, block_size, window, scale, max_query_len,
-                           query_start=None, max_seq_len=None):
+                           query_start=None, max_seq_len=None, out_cols=0):
     from ._lib import LatentAttnArgs
     T = q_lat.shape[0]
     if query_start is None:
@@ -222,7 +222,7 @@ def latent_attention_paged(q_lat, cache, positions, token_seq, block_tables, sin
     a.q_lat, a.latent_cache, a.out = _p(q_lat), _p(cache), _p(out)
     a.positions, a.token_seq, a.query_start, a.block_tables, a.sink = _p(positions), _p(token_seq), _p(query_start), _p(block_tables), _p(sink)
     a.T, a.B, a.max_blocks, a.H, a.R, a.block_size, a.window = T, block_tables.shape[0], block_tables.shape[1], H, R, block_size, window
-    a.scale, a.dtype, a.max_query_len, a.max_seq_len = scale, _CODES[cache.dtype], max_query_len, int(max_seq_len)
+    a.scale, a.dtype, a.max_query_len, a.max_seq_len, a.out_cols = scale, _CODES[cache.dtype], max_query_len, int(max_seq_len), out_cols
     _lib.lib().atoma_latent_attention_paged(C.byref(a), _s())
     _check()
     return out

@@ -76,10 +76,11 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4],
                     help="BASELINE.json configs: 2 (default) is the headline; 1, 3, 4 are the other measured configurations")
-    ap.add_argument("--design", default="llama", choices=["llama", "lilovik", "patadra", "nemasun"],
+    ap.add_argument("--design", default="llama", choices=["llama", "lilovik", "patadra", "nemasun", "surinex"],
                     help="llama (default): the headline workload; lilovik: the hybrid design's prefill / decode throughput and kernel "
                          "rooflines beside Llama at equal sizes (bench_hybrid.py); patadra: the same for the latent-attention / mixture-of-experts "
-                         "design (bench_patadra.py); nemasun: the same for the design on residual lanes (bench_nemasun.py)")
+                         "design (bench_patadra.py); nemasun: the same for the design on residual lanes (bench_nemasun.py); surinex: the same for the design of parallel blocks with "
+                         "matrix-state recurrences, beside Lilovik at equal sizes (bench_surinex.py)")
     ap.add_argument("--layers", type=int, default=0, help="debug only; the reported config needs the model's own layer count")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch between our kernels")
@@ -515,6 +516,9 @@ def main():
     if args.design == "nemasun":
         import bench_nemasun
         return bench_nemasun.run(args, torch, dev, json_fd)
+    if args.design == "surinex":
+        import bench_surinex
+        return bench_surinex.run(args, torch, dev, json_fd)
     if args.config == 3:
         import bench_mixed
         return bench_mixed.run(args, torch, dev, json_fd)

@@ -220,6 +220,8 @@ typedef struct atoma_latent_attn_args {
     uint32_t dtype;
     int32_t max_query_len, max_seq_len;
     int32_t skip_min_q;           /* > 0: sequences with at least this many query tokens in the step are left alone */
+    int64_t out_cols;             /* > 0: only the first out_cols entries of every row of `out` are read by the caller (a cached row whose
+                                   * tail takes part in the scores only, like a rotated key part); the rest may be left unwritten */
 } atoma_latent_attn_args;
 void atoma_latent_attention_paged(const atoma_latent_attn_args *args, atoma_stream_t stream);
 
