@@ -177,53 +177,103 @@ __global__ void __launch_bounds__(64 * kScanWarps) state_scan_kernel(const atoma
     const int q0 = a.query_start[b], n = a.query_start[b + 1] - q0;
     if (n <= 0) return;
     const int per_tok = (KIND == 0 ? 3 : 2) * DS + COLS + 4;     // q, k, (decay per channel), v of the CTA's columns, beta and decay
-    float *bufs[2] = {sm, sm + chunk * per_tok};
     for (int i = threadIdx.x; i < 2 * chunk * per_tok; i += blockDim.x) sm[i] = 0.f;   // what lies beyond dim stays zero
     const int kvh = KIND == 1 ? h / (H / static_cast<int>(a.G)) : h;
     const T *qp = static_cast<const T *>(a.q), *kp = static_cast<const T *>(a.k), *vp = static_cast<const T *>(a.v);
     const int jb = blockIdx.x * COLS;
     const bool loader = warp >= kScanWarps;
     // ---- staging (all warps for the first chunk, the staging warps afterwards) ----
+    // A warp takes TU tokens at a time: every load of the TU tokens is issued before the first value is used, so a chunk costs a
+    // few round trips to memory, not one per token.  Lane l holds elements l, l + 32, ... of a token's q / k / decay rows; the sums
+    // of squares run over a lane's elements in index order, then over the lanes by xor-shuffles: the same order for every token,
+    // wherever it falls in a chunk or a batch.
+    constexpr int EPL = RPT * PW / 32;                           // elements of a row per lane
+    constexpr int TU = EPL <= 4 ? 4 : (EPL == 8 ? 2 : 1);
+    const int vcol = (lane < COLS && jb + lane < V) ? jb + lane : -1;
+    float zb[EPL];                                               // what does not change from token to token
+    float neg_rate = 0.f, dtb = 0.f;
+    if (KIND == 0) {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) zb[e] = lane + 32 * e < D ? a.z_bias[h * D + lane + 32 * e] : 0.f;
+    } else {
+        neg_rate = -expf(a.a_log[h]);
+        dtb = a.dt_bias[h];
+    }
+    const float inv_tau = 1.0f / a.tau;
     auto stage = [&](int t0, float *buf, int w, int nw) {
         const int nt = min(chunk, n - t0);
-        for (int tk = w; tk < nt; tk += nw) {
-            const int64_t t = q0 + t0 + tk;
-            float *row = buf + tk * per_tok;
-            if (KIND == 0) {
-                for (int i = lane; i < D; i += 32) {
-                    const int o = (i / RPT) * (RPT + 4) + i % RPT;
-                    row[o] = to_f(qp[t * a.ld_q + h * D + i]) * a.q_scale;
-                    row[DS + o] = to_f(kp[t * a.ld_k + h * D + i]);
-                    const float z = to_f(static_cast<const T *>(a.z)[t * a.ld_z + h * D + i]) + a.z_bias[h * D + i];
-                    row[2 * DS + o] = expf(log_sigmoid(z) / a.tau);
+        for (int tk0 = w * TU; tk0 < nt; tk0 += nw * TU) {
+            // every address is valid (a token beyond the chunk reads the chunk's last, an element beyond dim reads element 0), so
+            // the loads carry no branches and all of them are in flight together
+            T qr[TU][EPL], kr[TU][EPL], zr[KIND == 0 ? TU : 1][KIND == 0 ? EPL : 1], vr[TU], br[TU], ar[TU];
+#pragma unroll
+            for (int u = 0; u < TU; ++u) {
+                const int64_t t = q0 + t0 + min(tk0 + u, nt - 1);
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) {
+                    const int i = lane + 32 * e < D ? lane + 32 * e : 0;
+                    qr[u][e] = qp[t * a.ld_q + kvh * D + i];
+                    kr[u][e] = kp[t * a.ld_k + kvh * D + i];
+                    if (KIND == 0) zr[u][e] = static_cast<const T *>(a.z)[t * a.ld_z + h * D + i];
                 }
-            } else {
-                float sq = 0.f, sk = 0.f;
-                for (int i = lane; i < D; i += 32) {
-                    const float qv = to_f(qp[t * a.ld_q + kvh * D + i]), kv = to_f(kp[t * a.ld_k + kvh * D + i]);
-                    sq = fmaf(qv, qv, sq);
-                    sk = fmaf(kv, kv, sk);
+                vr[u] = vp[t * a.ld_v + h * V + max(vcol, 0)];
+                if (KIND == 1) {
+                    br[u] = static_cast<const T *>(a.b_pre)[t * a.ld_b + h];
+                    ar[u] = static_cast<const T *>(a.a_pre)[t * a.ld_a + h];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < TU; ++u) {
+                if (tk0 + u >= nt) break;
+                float *row = buf + (tk0 + u) * per_tok;
+                float qv[EPL], kv[EPL];
+                float sq = 0.f, sk = 0.f, dot = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) {
+                    const bool in = lane + 32 * e < D;
+                    qv[e] = in ? to_f(qr[u][e]) : 0.f;
+                    kv[e] = in ? to_f(kr[u][e]) : 0.f;
+                    sq = fmaf(qv[e], qv[e], sq);
+                    sk = fmaf(kv[e], kv[e], sk);
+                    dot = fmaf(qv[e], kv[e], dot);
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) {
-                    sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                    sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                    if (KIND == 1) {
+                        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                        sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                    }
+                    dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 }
-                const float iq = a.q_scale / sqrtf(sq + a.unit_eps), ik = 1.0f / sqrtf(sk + a.unit_eps);
-                for (int i = lane; i < D; i += 32) {
-                    const int o = (i / RPT) * (RPT + 4) + i % RPT;
-                    row[o] = to_f(qp[t * a.ld_q + kvh * D + i]) * iq;
-                    row[DS + o] = to_f(kp[t * a.ld_k + kvh * D + i]) * ik;
+                float fq = a.q_scale, fk = 1.f;
+                if (KIND == 1) {
+                    fq = a.q_scale / sqrtf(sq + a.unit_eps);     // unit length per head, the query scaled
+                    fk = 1.0f / sqrtf(sk + a.unit_eps);
                 }
                 if (lane == 0) {
-                    const float bp = to_f(static_cast<const T *>(a.b_pre)[t * a.ld_b + h]);
-                    const float ap = to_f(static_cast<const T *>(a.a_pre)[t * a.ld_a + h]) + a.dt_bias[h];
-                    row[per_tok - 4] = sigmoidf_(bp);
-                    row[per_tok - 3] = expf(-expf(a.a_log[h]) * softplusf_(ap));
+                    if (KIND == 1) {
+                        row[per_tok - 4] = sigmoidf_(to_f(br[u]));
+                        row[per_tok - 3] = expf(neg_rate * softplusf_(to_f(ar[u]) + dtb));
+                    }
+                    row[per_tok - 2] = dot * fq * fk;            // q . k of the token as the recurrence sees them
                 }
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) {
+                    const int i = lane + 32 * e;
+                    if (i < D) {
+                        const int o = (i / RPT) * (RPT + 4) + i % RPT;
+                        if (KIND == 0) {
+                            const float decay = expf(log_sigmoid(to_f(zr[u][e]) + zb[e]) * inv_tau);
+                            row[o] = qv[e] * fq * decay;         // the read-out of the updated state, written on the old one (see below)
+                            row[2 * DS + o] = decay;
+                        } else {
+                            row[o] = qv[e] * fq;
+                        }
+                        row[DS + o] = kv[e] * fk;
+                    }
+                }
+                if (lane < COLS) row[(KIND == 0 ? 3 : 2) * DS + lane] = vcol >= 0 ? to_f(vr[u]) : 0.f;
             }
-            float *vrow = row + (KIND == 0 ? 3 : 2) * DS;
-            for (int c = lane; c < COLS; c += 32) vrow[c] = jb + c < V ? to_f(vp[t * a.ld_v + h * V + jb + c]) : 0.f;
         }
     };
     // ---- the state of this lane: rows part * RPT + r of column j ----
@@ -239,13 +289,13 @@ __global__ void __launch_bounds__(64 * kScanWarps) state_scan_kernel(const atoma
         }
     }
     __syncthreads();                                         // the zero fill is done
-    stage(0, bufs[0], warp, 2 * kScanWarps);
+    stage(0, sm, warp, 2 * kScanWarps);
     __syncthreads();
     int it = 0;
     for (int t0 = 0; t0 < n; t0 += chunk, ++it) {
-        float *buf = bufs[it & 1];
+        const float *buf = sm + (it & 1) * chunk * per_tok;
         if (loader) {
-            if (t0 + chunk < n) stage(t0 + chunk, bufs[(it + 1) & 1], warp - kScanWarps, kScanWarps);
+            if (t0 + chunk < n) stage(t0 + chunk, sm + ((it + 1) & 1) * chunk * per_tok, warp - kScanWarps, kScanWarps);
         } else {
             const int nt = min(chunk, n - t0);
             for (int tk = 0; tk < nt; ++tk) {
@@ -254,52 +304,58 @@ __global__ void __launch_bounds__(64 * kScanWarps) state_scan_kernel(const atoma
                 const float4 *kr = reinterpret_cast<const float4 *>(row + DS + part * (RPT + 4));
                 const float vj = row[(KIND == 0 ? 3 : 2) * DS + (warp % kScanWarps) * CW + lane % CW];
                 float o;
+                // Both recurrences read the state AFTER the token's write.  With S' = A S + k w^T (A the decay, w the written row):
+                // S'^T q = S^T (A q) + (k . q) w, so the sums over the rows run on the state as the previous token left it and the
+                // write is the only step between two tokens.  Four partial sums per lane (elements 4m .. 4m + 3 of its rows),
+                // added as (0 + 1) + (2 + 3), then over the lanes of the column: one fixed order.
+                const float kq = row[per_tok - 2];
                 if (KIND == 0) {
                     const float4 *ar = reinterpret_cast<const float4 *>(row + 2 * DS + part * (RPT + 4));
-                    float acc = 0.f;
+                    float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
 #pragma unroll
                     for (int r4 = 0; r4 < RPT / 4; ++r4) {
-                        const float4 a4 = ar[r4], k4 = kr[r4], q4 = qr[r4];
+                        const float4 a4 = ar[r4], k4 = kr[r4], q4 = qr[r4];     // q4: the query times the decay
+                        c0 = fmaf(S[4 * r4], q4.x, c0);
                         S[4 * r4] = fmaf(a4.x, S[4 * r4], k4.x * vj);
-                        acc = fmaf(S[4 * r4], q4.x, acc);
+                        c1 = fmaf(S[4 * r4 + 1], q4.y, c1);
                         S[4 * r4 + 1] = fmaf(a4.y, S[4 * r4 + 1], k4.y * vj);
-                        acc = fmaf(S[4 * r4 + 1], q4.y, acc);
+                        c2 = fmaf(S[4 * r4 + 2], q4.z, c2);
                         S[4 * r4 + 2] = fmaf(a4.z, S[4 * r4 + 2], k4.z * vj);
-                        acc = fmaf(S[4 * r4 + 2], q4.z, acc);
+                        c3 = fmaf(S[4 * r4 + 3], q4.w, c3);
                         S[4 * r4 + 3] = fmaf(a4.w, S[4 * r4 + 3], k4.w * vj);
-                        acc = fmaf(S[4 * r4 + 3], q4.w, acc);
                     }
-                    o = parts_sum<PW>(acc);
+                    o = fmaf(kq, vj, parts_sum<PW>((c0 + c1) + (c2 + c3)));
                 } else {
                     const float beta = row[per_tok - 4], g = row[per_tok - 3];
-                    float acc = 0.f;
-#pragma unroll
-                    for (int r4 = 0; r4 < RPT / 4; ++r4) {
-                        const float4 k4 = kr[r4];
-                        S[4 * r4] *= g;
-                        acc = fmaf(S[4 * r4], k4.x, acc);
-                        S[4 * r4 + 1] *= g;
-                        acc = fmaf(S[4 * r4 + 1], k4.y, acc);
-                        S[4 * r4 + 2] *= g;
-                        acc = fmaf(S[4 * r4 + 2], k4.z, acc);
-                        S[4 * r4 + 3] *= g;
-                        acc = fmaf(S[4 * r4 + 3], k4.w, acc);
-                    }
-                    const float u = beta * (vj - parts_sum<PW>(acc));
-                    acc = 0.f;
+                    float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f, d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
                     for (int r4 = 0; r4 < RPT / 4; ++r4) {
                         const float4 k4 = kr[r4], q4 = qr[r4];
-                        S[4 * r4] = fmaf(k4.x, u, S[4 * r4]);
-                        acc = fmaf(S[4 * r4], q4.x, acc);
-                        S[4 * r4 + 1] = fmaf(k4.y, u, S[4 * r4 + 1]);
-                        acc = fmaf(S[4 * r4 + 1], q4.y, acc);
-                        S[4 * r4 + 2] = fmaf(k4.z, u, S[4 * r4 + 2]);
-                        acc = fmaf(S[4 * r4 + 2], q4.z, acc);
-                        S[4 * r4 + 3] = fmaf(k4.w, u, S[4 * r4 + 3]);
-                        acc = fmaf(S[4 * r4 + 3], q4.w, acc);
+                        c0 = fmaf(S[4 * r4], k4.x, c0);
+                        d0 = fmaf(S[4 * r4], q4.x, d0);
+                        c1 = fmaf(S[4 * r4 + 1], k4.y, c1);
+                        d1 = fmaf(S[4 * r4 + 1], q4.y, d1);
+                        c2 = fmaf(S[4 * r4 + 2], k4.z, c2);
+                        d2 = fmaf(S[4 * r4 + 2], q4.z, d2);
+                        c3 = fmaf(S[4 * r4 + 3], k4.w, c3);
+                        d3 = fmaf(S[4 * r4 + 3], q4.w, d3);
                     }
-                    o = parts_sum<PW>(acc);
+                    float sk = (c0 + c1) + (c2 + c3), sq = (d0 + d1) + (d2 + d3);
+#pragma unroll
+                    for (int x = 32 / PW; x < 32; x <<= 1) {
+                        sk += __shfl_xor_sync(0xffffffffu, sk, x);
+                        sq += __shfl_xor_sync(0xffffffffu, sq, x);
+                    }
+                    const float u = beta * (vj - g * sk);        // the decayed state's answer to k
+                    o = fmaf(g, sq, u * kq);
+#pragma unroll
+                    for (int r4 = 0; r4 < RPT / 4; ++r4) {
+                        const float4 k4 = kr[r4];
+                        S[4 * r4] = fmaf(g, S[4 * r4], k4.x * u);
+                        S[4 * r4 + 1] = fmaf(g, S[4 * r4 + 1], k4.y * u);
+                        S[4 * r4 + 2] = fmaf(g, S[4 * r4 + 2], k4.z * u);
+                        S[4 * r4 + 3] = fmaf(g, S[4 * r4 + 3], k4.w * u);
+                    }
                 }
                 if (part == 0 && j < V) a.out[static_cast<int64_t>(q0 + t0 + tk) * H * V + h * V + j] = o;
             }
