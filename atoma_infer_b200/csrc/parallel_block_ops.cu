@@ -20,6 +20,7 @@
 
 namespace atoma {
 
+extern int g_hybrid_debug;   // bit 1: general kernels only
 bool hyb_head_project_ld(const void *, int64_t, int64_t, const void *, void *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int32_t,
                          uint32_t, cudaStream_t);   // latent_attention.cu
 
@@ -116,6 +117,111 @@ __global__ void __launch_bounds__(256) tap_filter_kernel(const atoma_tap_filter_
         if (a.residual) f2 += cur;
         if (a.act == 1) f2 = silu(f2);
         static_cast<T *>(a.out2)[t * a.ld_out + c] = from_f<T>(f2);
+    }
+}
+
+// The same filter for bfloat16 rows of 16-byte pieces: a thread owns 8 neighbouring channels and `run` consecutive tokens, keeps
+// the filters' weights and the last TAPS - 1 inputs in registers, and slides that window from token to token; it is filled anew
+// at the run's first token and wherever a portion starts (from the rows before, the sequence's carried inputs, or zeros).
+// Per element the products are added in the order of the kernel above, so both give the same bits.
+template <int TAPS>
+__global__ void __launch_bounds__(128) tap_filter_vec_kernel(const atoma_tap_filter_args a, int run) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int C = static_cast<int>(a.channels), T = static_cast<int>(a.T);
+    const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c0 >= C) return;
+    const int t_first = blockIdx.y * run, t_end = min(T, t_first + run);
+    const __nv_bfloat16 *in = static_cast<const __nv_bfloat16 *>(a.in);
+    float w1[8][TAPS], w2[8][TAPS];
+    {
+        const float4 *p1 = reinterpret_cast<const float4 *>(a.w1 + static_cast<int64_t>(c0) * TAPS);
+        const float4 *p2 = a.w2 ? reinterpret_cast<const float4 *>(a.w2 + static_cast<int64_t>(c0) * TAPS) : p1;
+#pragma unroll
+        for (int i = 0; i < 2 * TAPS; ++i) {
+            const float4 x = p1[i], y = p2[i];
+            const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                w1[(4 * i + e) / TAPS][(4 * i + e) % TAPS] = xs[e];
+                w2[(4 * i + e) / TAPS][(4 * i + e) % TAPS] = ys[e];
+            }
+        }
+    }
+    auto row8 = [&](int64_t t, float *v) {
+        const uint4 r = *reinterpret_cast<const uint4 *>(in + t * a.ld_in + c0);
+        const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            v[2 * e] = __uint_as_float(u[e] << 16);
+            v[2 * e + 1] = __uint_as_float(u[e] & 0xffff0000u);
+        }
+    };
+    float win[TAPS > 1 ? TAPS - 1 : 1][8];                     // win[k]: the input TAPS - 1 - k tokens back
+    for (int t = t_first; t < t_end; ++t) {
+        const int b = a.token_seq[t];
+        const int i = t - a.query_start[b];
+        if (TAPS > 1 && (t == t_first || i == 0)) {
+            const int ctx = a.context_lens[b];
+            const float *hist = a.history ? a.history + static_cast<int64_t>(a.state_slots[b]) * a.history_stride : nullptr;
+#pragma unroll
+            for (int k = 0; k < TAPS - 1; ++k) {
+                const int back = TAPS - 1 - k;
+                if (i - back >= 0) {
+                    row8(t - back, win[k]);
+                } else if (ctx + i - back >= 0 && hist) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) win[k][e] = hist[static_cast<int64_t>(TAPS - 1 + i - back) * C + c0 + e];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) win[k][e] = 0.f;
+                }
+            }
+        }
+        float cur[8], f1[8], f2[8];
+        row8(t, cur);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float x = 0.f, y = 0.f;
+#pragma unroll
+            for (int k = 0; k < TAPS - 1; ++k) {
+                x = fmaf(w1[e][k], win[k][e], x);
+                y = fmaf(w2[e][k], win[k][e], y);
+            }
+            x = fmaf(w1[e][TAPS - 1], cur[e], x);
+            y = fmaf(w2[e][TAPS - 1], cur[e], y);
+            if (a.residual) {
+                x += cur[e];
+                y += cur[e];
+            }
+            if (a.act == 1) {
+                x = silu(x);
+                y = silu(y);
+            }
+            f1[e] = x;
+            f2[e] = y;
+        }
+        uint4 o;
+        o.x = pack2<__nv_bfloat16>(f1[0], f1[1]);
+        o.y = pack2<__nv_bfloat16>(f1[2], f1[3]);
+        o.z = pack2<__nv_bfloat16>(f1[4], f1[5]);
+        o.w = pack2<__nv_bfloat16>(f1[6], f1[7]);
+        *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(a.out1) + static_cast<int64_t>(t) * a.ld_out + c0) = o;
+        if (a.w2) {
+            o.x = pack2<__nv_bfloat16>(f2[0], f2[1]);
+            o.y = pack2<__nv_bfloat16>(f2[2], f2[3]);
+            o.z = pack2<__nv_bfloat16>(f2[4], f2[5]);
+            o.w = pack2<__nv_bfloat16>(f2[6], f2[7]);
+            *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(a.out2) + static_cast<int64_t>(t) * a.ld_out + c0) = o;
+        }
+#pragma unroll
+        for (int k = 0; k + 1 < TAPS - 1; ++k)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) win[k][e] = win[k + 1][e];
+        if (TAPS > 1) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) win[TAPS - 2][e] = cur[e];
+        }
     }
 }
 
@@ -588,9 +694,23 @@ bool hyb_tap_filter(const atoma_tap_filter_args &a, cudaStream_t stream) {
         return false;
     }
     const unsigned cb = static_cast<unsigned>((a.channels + 255) / 256);
+    auto piece16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = a.dtype == ATOMA_DTYPE_BF16 && a.taps >= 2 && a.taps <= 4 && a.channels % 8 == 0 && a.ld_in % 8 == 0 && a.ld_out % 8 == 0 &&
+                     piece16(a.in) && piece16(a.out1) && piece16(a.out2) && piece16(a.w1) && piece16(a.w2) && !(g_hybrid_debug & 2);
+    if (vec) {
+        // tokens per thread: long steps amortise the window's refill, short ones keep the device filled
+        const int run = a.T >= 4096 ? 16 : (a.T >= 1024 ? 8 : (a.T >= 256 ? 4 : 1));
+        const dim3 grid(static_cast<unsigned>((a.channels / 8 + 127) / 128), static_cast<unsigned>((a.T + run - 1) / run));
+        cudaError_t e;
+        if (a.taps == 2) e = launch_ex(tap_filter_vec_kernel<2>, grid, dim3(128), 0, stream, a, run);
+        else if (a.taps == 3) e = launch_ex(tap_filter_vec_kernel<3>, grid, dim3(128), 0, stream, a, run);
+        else e = launch_ex(tap_filter_vec_kernel<4>, grid, dim3(128), 0, stream, a, run);
+        if (!hybrid::launched(e, "tap_filter_vec_kernel")) return false;
+    } else {
 #define CALL(TT) launch_ex(tap_filter_kernel<TT>, dim3(cb, static_cast<unsigned>(a.T)), dim3(256), 0, stream, a)
-    if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "tap_filter_kernel")) return false;
+        if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "tap_filter_kernel")) return false;
 #undef CALL
+    }
     if (a.taps == 1) return true;
 #define CALL(TT) launch_ex(tap_history_kernel<TT>, dim3(cb, static_cast<unsigned>(a.B)), dim3(256), 0, stream, a)
     return hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "tap_history_kernel");

@@ -118,6 +118,45 @@ def test_tap_filters_over_portions_of_any_size(dtype, taps, C, residual, act):
         step += 1
 
 
+@pytest.mark.parametrize("taps,act", [(2, 0), (3, 1), (4, 0)])
+@pytest.mark.parametrize("counts", [[700, 3, 1, 520, 77], [2500, 1, 1700, 13]])
+def test_tap_filters_on_long_steps(taps, act, counts):
+    """Long steps, where a thread walks several tokens with the last inputs in registers: portions that start in the middle of a
+    thread's run, sequences that continue from carried inputs beside fresh ones, against the plain filter over the whole sequences,
+    and bit for bit against the kernel that reads every input anew."""
+    C = 72
+    g = torch.Generator().manual_seed(taps + len(counts))
+    before = [5, 0, 1, 0, 2][:len(counts)]                   # tokens of each sequence that an earlier step brought
+    xs = [bf(rnd(g, b + n, C)) for b, n in zip(before, counts)]
+    w1, w2 = rnd(g, C, taps, scale=0.5), rnd(g, C, taps, scale=0.5)
+    residual = not act
+
+    def whole(x, w):
+        y = so.causal_taps(x.double(), w.double())
+        y = x.double() + y if residual else y
+        return so.silu(y) if act else y
+
+    outs = []
+    for flags in (0, 2):
+        _ops().debug_flags(flags)
+        hist = torch.full((len(counts), (taps - 1) * C), 55.0, device=DEV)
+        slots = i32(list(range(len(counts)))[::-1])
+        first = [b for b in range(len(counts)) if before[b]]
+        tseq, qs = batch_layout([before[b] for b in first])
+        x0 = torch.cat([xs[b][:before[b]] for b in first]).to(torch.bfloat16).to(DEV)
+        _ops().tap_filter(x0, w1.to(DEV), w2.to(DEV), hist, slots[first], tseq, qs, i32([0] * len(first)), residual, act)
+        tseq, qs = batch_layout(counts)
+        x = torch.cat([xs[b][before[b]:] for b in range(len(counts))]).to(torch.bfloat16).to(DEV)
+        outs.append(_ops().tap_filter(x, w1.to(DEV), w2.to(DEV), hist, slots, tseq, qs, i32(before), residual, act))
+    (a1, a2), (b1, b2) = outs
+    assert torch.equal(a1, b1) and torch.equal(a2, b2)
+    at = 0
+    for b, n in enumerate(counts):
+        assert nerr(a1[at:at + n], whole(xs[b], w1)[before[b]:]) < 8e-3, b
+        assert nerr(a2[at:at + n], whole(xs[b], w2)[before[b]:]) < 8e-3, b
+        at += n
+
+
 # ------------------------------------------------------------------------------------------------
 # matrix-state recurrences
 # ------------------------------------------------------------------------------------------------
