@@ -20,7 +20,7 @@
 
 namespace atoma {
 
-extern int g_hybrid_debug;   // bit 1: general kernels only
+extern int g_hybrid_debug;   // bit 1: general kernels only; bit 4: scans with many rows per lane
 bool hyb_head_project_ld(const void *, int64_t, int64_t, const void *, void *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int32_t,
                          uint32_t, cudaStream_t);   // latent_attention.cu
 
@@ -262,6 +262,8 @@ __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log
 // norms of q and k) into the other buffer; one barrier per chunk.
 // Staged row of a token: element i of q / k / decay at (i / RPT) * (RPT + 4) + i % RPT — a lane's RPT values are contiguous and
 // 16-byte aligned (float4 loads), and the PW lanes of a column read distinct banks.
+// Two splits per key size: many rows per lane (few instructions per state entry: steps with many CTAs) and 8 rows per lane (a
+// short chain per token and four times the warps: steps with few).  Both add in the same order, so they give the same bits.
 constexpr int kScanWarps = 4;
 
 template <int PW>
@@ -272,7 +274,7 @@ __device__ __forceinline__ float parts_sum(float v) {
 }
 
 template <typename T, int KIND, int RPT, int PW>
-__global__ void __launch_bounds__(64 * kScanWarps) state_scan_kernel(const atoma_state_scan_args a, int chunk) {
+__global__ void __launch_bounds__(64 * kScanWarps, 2) state_scan_kernel(const atoma_state_scan_args a, int chunk) {
     extern __shared__ __align__(16) float sm[];
     constexpr int CW = 32 / PW, COLS = CW * kScanWarps, DS = PW * (RPT + 4);
     pdl_launch_dependents();
@@ -412,41 +414,66 @@ __global__ void __launch_bounds__(64 * kScanWarps) state_scan_kernel(const atoma
                 float o;
                 // Both recurrences read the state AFTER the token's write.  With S' = A S + k w^T (A the decay, w the written row):
                 // S'^T q = S^T (A q) + (k . q) w, so the sums over the rows run on the state as the previous token left it and the
-                // write is the only step between two tokens.  Four partial sums per lane (elements 4m .. 4m + 3 of its rows),
-                // added as (0 + 1) + (2 + 3), then over the lanes of the column: one fixed order.
+                // write is the only step between two tokens.
+                // Order of a sum over the rows, the same for every split of the rows over lanes: groups of 8 rows (four partial sums
+                // over rows m, m + 4, added as (0 + 1) + (2 + 3)), then a binary tree over the groups — inside a lane first, then by
+                // xor-shuffles over the lanes of the column.
+                constexpr int G8 = RPT / 8;
                 const float kq = row[per_tok - 2];
                 if (KIND == 0) {
                     const float4 *ar = reinterpret_cast<const float4 *>(row + 2 * DS + part * (RPT + 4));
-                    float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+                    float gs[G8];
 #pragma unroll
-                    for (int r4 = 0; r4 < RPT / 4; ++r4) {
-                        const float4 a4 = ar[r4], k4 = kr[r4], q4 = qr[r4];     // q4: the query times the decay
-                        c0 = fmaf(S[4 * r4], q4.x, c0);
-                        S[4 * r4] = fmaf(a4.x, S[4 * r4], k4.x * vj);
-                        c1 = fmaf(S[4 * r4 + 1], q4.y, c1);
-                        S[4 * r4 + 1] = fmaf(a4.y, S[4 * r4 + 1], k4.y * vj);
-                        c2 = fmaf(S[4 * r4 + 2], q4.z, c2);
-                        S[4 * r4 + 2] = fmaf(a4.z, S[4 * r4 + 2], k4.z * vj);
-                        c3 = fmaf(S[4 * r4 + 3], q4.w, c3);
-                        S[4 * r4 + 3] = fmaf(a4.w, S[4 * r4 + 3], k4.w * vj);
+                    for (int g8 = 0; g8 < G8; ++g8) {
+                        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int r4 = 2 * g8; r4 < 2 * g8 + 2; ++r4) {
+                            const float4 a4 = ar[r4], k4 = kr[r4], q4 = qr[r4];     // q4: the query times the decay
+                            c[0] = fmaf(S[4 * r4], q4.x, c[0]);
+                            S[4 * r4] = fmaf(a4.x, S[4 * r4], k4.x * vj);
+                            c[1] = fmaf(S[4 * r4 + 1], q4.y, c[1]);
+                            S[4 * r4 + 1] = fmaf(a4.y, S[4 * r4 + 1], k4.y * vj);
+                            c[2] = fmaf(S[4 * r4 + 2], q4.z, c[2]);
+                            S[4 * r4 + 2] = fmaf(a4.z, S[4 * r4 + 2], k4.z * vj);
+                            c[3] = fmaf(S[4 * r4 + 3], q4.w, c[3]);
+                            S[4 * r4 + 3] = fmaf(a4.w, S[4 * r4 + 3], k4.w * vj);
+                        }
+                        gs[g8] = (c[0] + c[1]) + (c[2] + c[3]);
                     }
-                    o = fmaf(kq, vj, parts_sum<PW>((c0 + c1) + (c2 + c3)));
+#pragma unroll
+                    for (int w = 1; w < G8; w <<= 1)
+#pragma unroll
+                        for (int g8 = 0; g8 < G8; g8 += 2 * w) gs[g8] += gs[g8 + w];
+                    o = fmaf(kq, vj, parts_sum<PW>(gs[0]));
                 } else {
                     const float beta = row[per_tok - 4], g = row[per_tok - 3];
-                    float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f, d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+                    float gk[G8], gq[G8];
 #pragma unroll
-                    for (int r4 = 0; r4 < RPT / 4; ++r4) {
-                        const float4 k4 = kr[r4], q4 = qr[r4];
-                        c0 = fmaf(S[4 * r4], k4.x, c0);
-                        d0 = fmaf(S[4 * r4], q4.x, d0);
-                        c1 = fmaf(S[4 * r4 + 1], k4.y, c1);
-                        d1 = fmaf(S[4 * r4 + 1], q4.y, d1);
-                        c2 = fmaf(S[4 * r4 + 2], k4.z, c2);
-                        d2 = fmaf(S[4 * r4 + 2], q4.z, d2);
-                        c3 = fmaf(S[4 * r4 + 3], k4.w, c3);
-                        d3 = fmaf(S[4 * r4 + 3], q4.w, d3);
+                    for (int g8 = 0; g8 < G8; ++g8) {
+                        float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int r4 = 2 * g8; r4 < 2 * g8 + 2; ++r4) {
+                            const float4 k4 = kr[r4], q4 = qr[r4];
+                            c[0] = fmaf(S[4 * r4], k4.x, c[0]);
+                            d[0] = fmaf(S[4 * r4], q4.x, d[0]);
+                            c[1] = fmaf(S[4 * r4 + 1], k4.y, c[1]);
+                            d[1] = fmaf(S[4 * r4 + 1], q4.y, d[1]);
+                            c[2] = fmaf(S[4 * r4 + 2], k4.z, c[2]);
+                            d[2] = fmaf(S[4 * r4 + 2], q4.z, d[2]);
+                            c[3] = fmaf(S[4 * r4 + 3], k4.w, c[3]);
+                            d[3] = fmaf(S[4 * r4 + 3], q4.w, d[3]);
+                        }
+                        gk[g8] = (c[0] + c[1]) + (c[2] + c[3]);
+                        gq[g8] = (d[0] + d[1]) + (d[2] + d[3]);
                     }
-                    float sk = (c0 + c1) + (c2 + c3), sq = (d0 + d1) + (d2 + d3);
+#pragma unroll
+                    for (int w = 1; w < G8; w <<= 1)
+#pragma unroll
+                        for (int g8 = 0; g8 < G8; g8 += 2 * w) {
+                            gk[g8] += gk[g8 + w];
+                            gq[g8] += gq[g8 + w];
+                        }
+                    float sk = gk[0], sq = gq[0];
 #pragma unroll
                     for (int x = 32 / PW; x < 32; x <<= 1) {
                         sk += __shfl_xor_sync(0xffffffffu, sk, x);
@@ -728,17 +755,26 @@ bool hyb_state_scan(const atoma_state_scan_args &a, cudaStream_t stream) {
         return false;
     }
     // rows of a column per lane (RPT) and lanes per column (PW): dim <= RPT * PW
-    const int rpt = a.dim <= 64 ? 16 : 32;
-    const int pw = a.dim <= 128 ? 4 : (a.dim <= 256 ? 8 : 16);
+    int rpt = a.dim <= 64 ? 16 : 32;
+    int pw = a.dim <= 128 ? 4 : (a.dim <= 256 ? 8 : 16);
     if (a.dim > 512) {
         set_status(kErrUnsupported, "atoma_state_scan: a key size of %lld exceeds 512", static_cast<long long>(a.dim));
         return false;
+    }
+    // few CTAs (one long prompt, a handful of decoded tokens): 8 rows per lane, so that a token is a short chain and the state's
+    // entries are spread over more warps — as long as all CTAs are resident at once (two per SM): a second wave would walk the
+    // tokens a second time
+    const int64_t ctas_many = (a.vdim + 32 / pw * kScanWarps - 1) / (32 / pw * kScanWarps) * a.H * a.B;
+    if (a.dim <= 256 && !(g_hybrid_debug & 16) && ctas_many * (rpt / 8) <= 2 * current_device_info().sm_count) {
+        pw = pw * rpt / 8;
+        rpt = 8;
     }
     const int cols = 32 / pw * kScanWarps;
     const int per_tok = (gla ? 3 : 2) * pw * (rpt + 4) + cols + 4;
     int64_t longest = a.T;                                   // a bound of the longest portion: T tokens over B sequences, each has one at least
     longest = std::max<int64_t>(1, a.T - (a.B - 1));
-    const int chunk = static_cast<int>(std::min<int64_t>(32, longest));
+    // staged tokens per buffer: at most 32, no more than the longest portion, and two CTAs' buffers fit one SM
+    const int chunk = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({32, longest, 96 * 1024 / (8 * per_tok)})));
     const size_t smem = static_cast<size_t>(2 * chunk * per_tok) * 4;
     const dim3 grid(static_cast<unsigned>((a.vdim + cols - 1) / cols), static_cast<unsigned>(a.H), static_cast<unsigned>(a.B));
     const dim3 block(64 * kScanWarps);
@@ -750,7 +786,10 @@ bool hyb_state_scan(const atoma_state_scan_args &a, cudaStream_t stream) {
     } while (0)
 #define SCAN_K(TT, KIND)                                \
     do {                                                \
-        if (rpt == 16) SCAN(TT, KIND, 16, 4);           \
+        if (rpt == 8 && pw == 8) SCAN(TT, KIND, 8, 8);  \
+        else if (rpt == 8 && pw == 16) SCAN(TT, KIND, 8, 16); \
+        else if (rpt == 8) SCAN(TT, KIND, 8, 32);       \
+        else if (rpt == 16) SCAN(TT, KIND, 16, 4);      \
         else if (pw == 4) SCAN(TT, KIND, 32, 4);        \
         else if (pw == 8) SCAN(TT, KIND, 32, 8);        \
         else SCAN(TT, KIND, 32, 16);                    \

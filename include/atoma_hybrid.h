@@ -687,7 +687,9 @@ void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_hybrid_batch
 
 /* Diagnostics: bit 0 = every projection through the plain float32-FMA kernel; bit 1 = the general attention kernel
  * for every batch (no tensor-core prefill / split decode kernels); bit 2 = the sequential minGRU scan; bit 3 = the routed
- * experts' tensor-memory (tcgen05) products for steps of any size (they normally serve steps of 1024 pairs and more). */
+ * experts' tensor-memory (tcgen05) products for steps of any size (they normally serve steps of 1024 pairs and more);
+ * bit 4 = the matrix-state scans with many rows per lane whatever the step's size (they normally take 8 rows per lane when a
+ * step has few CTAs; both add in the same order). */
 void atoma_debug_hybrid(int flags);
 
 #ifdef __cplusplus

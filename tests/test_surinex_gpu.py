@@ -177,8 +177,10 @@ def scan_steps(cuts, lens, run):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("H,D,V,tau", [(2, 16, 24, 8.0), (3, 48, 40, 16.0), (1, 80, 72, 4.0), (2, 130, 32, 2.0), (4, 8, 5, 1.0)])
-def test_gated_linear_attention_recurrence(dtype, H, D, V, tau):
+@pytest.mark.parametrize("rows", [0, 16])                  # 8 rows of the state per lane (steps of few CTAs) / many
+@pytest.mark.parametrize("H,D,V,tau", [(2, 16, 24, 8.0), (3, 48, 40, 16.0), (1, 80, 72, 4.0), (2, 130, 32, 2.0), (4, 8, 5, 1.0), (1, 300, 9, 3.0)])
+def test_gated_linear_attention_recurrence(dtype, rows, H, D, V, tau):
+    _ops().debug_flags(rows)
     g = torch.Generator().manual_seed(H * 1000 + D)
     lens, cuts, slots = [37, 12], [[1, 20, 2, 14], [12]], [3, 1]
     qs_, ks_, vs_, zs_ = ([rnd(g, n, H * d_, scale=s) for n in lens] for d_, s in ((D, 1.0), (D, 0.5), (V, 1.0), (D, 2.0)))
@@ -202,8 +204,10 @@ def test_gated_linear_attention_recurrence(dtype, H, D, V, tau):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("H,G,D,V", [(4, 2, 16, 24), (2, 1, 32, 32), (3, 3, 80, 40), (6, 2, 48, 72), (2, 2, 130, 8)])
-def test_gated_delta_rule_recurrence(dtype, H, G, D, V):
+@pytest.mark.parametrize("rows", [0, 16])
+@pytest.mark.parametrize("H,G,D,V", [(4, 2, 16, 24), (2, 1, 32, 32), (3, 3, 80, 40), (6, 2, 48, 72), (2, 2, 130, 8), (1, 1, 260, 6)])
+def test_gated_delta_rule_recurrence(dtype, rows, H, G, D, V):
+    _ops().debug_flags(rows)
     g = torch.Generator().manual_seed(H * 1000 + D + 7)
     lens, cuts, slots = [41, 10], [[2, 1, 30, 8], [10]], [0, 2]
     qs_, ks_, vs_ = ([rnd(g, n, c) for n in lens] for c in (G * D, G * D, H * V))
@@ -225,6 +229,33 @@ def test_gated_delta_rule_recurrence(dtype, H, G, D, V):
 
     for got, w in zip(scan_steps(cuts, lens, run), want):
         assert nerr(got, w) < 2e-5
+
+
+@pytest.mark.parametrize("kind,D", [("gla", 48), ("gla", 128), ("gla", 200), ("delta", 64), ("delta", 128), ("delta", 256)])
+def test_both_splits_of_the_state_over_lanes_give_the_same_bits(kind, D):
+    """A step of few CTAs spreads the rows of a column over more lanes than a step of many; a request's numbers must not depend on
+    which one served it.  One 70-token portion after a 3-token one, outputs and carried state compared bit for bit."""
+    H, G, V, n = 2, 1, 24, 73
+    g = torch.Generator().manual_seed(D)
+    outs = []
+    q, k = (rnd(g, n, (H if kind == "gla" else G) * D).to(torch.bfloat16).to(DEV) for _ in range(2))
+    v, z = rnd(g, n, H * V).to(torch.bfloat16).to(DEV), rnd(g, n, H * D, scale=2.0).to(torch.bfloat16).to(DEV)
+    bp, ap = rnd(g, n, H).to(torch.bfloat16).to(DEV), rnd(g, n, H).to(torch.bfloat16).to(DEV)
+    zb, al, dt = rnd(g, H * D, shift=2.0).to(DEV), rnd(g, H, scale=0.5, shift=-1.0).to(DEV), rnd(g, H, scale=0.5).to(DEV)
+    for flags in (0, 16):
+        _ops().debug_flags(flags)
+        state = torch.full((1, H * D * V), 4.0, device=DEV)
+        got = []
+        for lo, hi in ((0, 3), (3, n)):
+            sl = slice(lo, hi)
+            if kind == "gla":
+                got.append(_ops().gla_scan(q[sl], k[sl], v[sl], z[sl], zb, 6.0, D ** -0.5, state, i32([0]), i32([0, hi - lo]), i32([lo]), H, D, V))
+            else:
+                got.append(_ops().delta_rule_scan(q[sl], k[sl], v[sl], bp[sl], ap[sl], al, dt, D ** -0.5, state, i32([0]), i32([0, hi - lo]),
+                                                  i32([lo]), H, G, D, V))
+        outs.append((torch.cat(got), state.clone()))
+    assert torch.isfinite(outs[0][0]).all()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
 
 
 def test_a_write_far_back_is_still_read():
@@ -295,7 +326,7 @@ def plain_rotary_sigmoid(q, k, v, qn, kn, pb, f_qk, f_v, layout, scale, H, G, D,
 
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("general", [False, True])
-@pytest.mark.parametrize("H,G,D,V,dims,layout,scaling", [(4, 2, 16, 24, 8, "interleaved", True), (6, 1, 64, 64, 16, "interleaved", True),
+@pytest.mark.parametrize("H,G,D,V,dims,layout,scaling", [(4, 2, 16, 24, 8, "interleaved", True), (8, 2, 64, 64, 24, "interleaved", True),
                                                           (3, 3, 10, 6, 10, "halves", False), (2, 1, 32, 16, 12, "halves", True),
                                                           (2, 2, 64, 64, 64, "interleaved", False)])
 def test_rotary_sigmoid_attention_on_a_mixed_batch(dtype, general, H, G, D, V, dims, layout, scaling):
@@ -373,7 +404,7 @@ def test_one_loud_key_far_back_carries_its_value_home(far, decode):
 # latent attention with a rotated key part
 # ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("H,D,Rd,V,Rq,Rk,dims,layout", [(3, 16, 8, 16, 24, 32, 8, "halves"), (8, 64, 32, 64, 80, 64, 32, "halves"),
+@pytest.mark.parametrize("H,D,Rd,V,Rq,Rk,dims,layout", [(3, 16, 8, 16, 24, 32, 8, "halves"), (6, 64, 32, 64, 72, 128, 32, "halves"),
                                                        (2, 10, 6, 12, 9, 14, 4, "interleaved"), (4, 32, 64, 48, 40, 128, 64, "halves")])
 def test_latent_attention_with_a_rotated_key_part(dtype, H, D, Rd, V, Rq, Rk, dims, layout):
     ops = _ops()
