@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(32 * MAXWARPS, (MAXWARPS == 8 && kPfKeys == 32
     }
     for (int i = threadIdx.x; i < hpc; i += nthreads) {
         bias_s[i] = a.head_bias[rank * hpc + i];
-        slope_s[i] = a.slopes[rank * hpc + i];
+        slope_s[i] = a.slopes ? a.slopes[rank * hpc + i] : 0.f;
     }
     const __nv_bfloat16 *kc = static_cast<const __nv_bfloat16 *>(a.k_cache);
     const __nv_bfloat16 *vc = static_cast<const __nv_bfloat16 *>(a.v_cache);

@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(kGenThreads) sigmoid_attn_general_kernel(const
                 float dot;
                 if (vec) dot = dot_row_vec(qh, reinterpret_cast<const __nv_bfloat16 *>(kr), D);
                 else dot = dot_row<T>(qh, kr, D);
-                w = sigmoid_weight(dot, a.scale, a.softcap, a.slopes[g], static_cast<float>(p - j), a.head_bias[g]);
+                w = sigmoid_weight(dot, a.scale, a.softcap, a.slopes ? a.slopes[g] : 0.f, static_cast<float>(p - j), a.head_bias[g]);
             }
             w_s[idx] = w;
         }
@@ -560,7 +560,7 @@ bool hyb_qk_norm_cache(const void *qkv, const float *bias, const float *q_w, con
 
 bool hyb_attention_check(const atoma_sigmoid_attn_args &a) {
     if (bad_dtype(a.dtype, "atoma_sigmoid_attention_paged")) return false;
-    if (!a.q || !a.k_cache || !a.v_cache || !a.out || !a.positions || !a.token_seq || !a.block_tables || !a.slopes ||
+    if (!a.q || !a.k_cache || !a.v_cache || !a.out || !a.positions || !a.token_seq || !a.block_tables ||
         !a.head_bias || a.H <= 0 || a.G <= 0 || a.H % a.G || a.dim <= 0 || a.vdim <= 0 || a.block_size <= 0 || a.max_blocks <= 0) {
         set_status(kErrInvalidArg, "atoma_sigmoid_attention_paged: null argument or inconsistent head counts");
         return false;
@@ -610,10 +610,17 @@ bool hyb_attn_split_reduce(const float *partial, void *out, int64_t T, int split
 }
 
 bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, bool *taken);   // hybrid_attention.cu
+bool hyb_sigmoid_attention_tc(const atoma_sigmoid_attn_args &a, cudaStream_t stream, bool *taken);   // softmax_attention_tc.cu
 
 bool hyb_attention(const atoma_sigmoid_attn_args &a, cudaStream_t stream) {
     if (a.T <= 0) return true;
     if (!hyb_attention_check(a)) return false;
+    if (!(g_hybrid_debug & 2) && !a.slopes && !a.talk && a.softcap == 0.f) {
+        // independent heads (no distance term, no cap, no talk): the warp-level tensor-core kernels that softmax attention uses
+        bool taken = false;
+        const bool ok = hyb_sigmoid_attention_tc(a, stream, &taken);
+        if (taken || !ok) return ok;
+    }
     if (!(g_hybrid_debug & 2)) {
         bool taken = false;
         const bool ok = hyb_attention_fast(a, stream, &taken);

@@ -684,7 +684,7 @@ bool parallel_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, co
         a.query_start = b.query_start;
         a.max_seq_len = b.max_seq_len;
         a.block_tables = b.block_tables;
-        a.slopes = l.slopes;
+        a.slopes = nullptr;               // no distance term, no talk between the heads: independent heads
         a.head_bias = l.head_bias;
         a.talk = nullptr;
         a.T = T;

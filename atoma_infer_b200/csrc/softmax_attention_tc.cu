@@ -54,8 +54,11 @@ __host__ __device__ inline TcLayout tc_layout(int D, int DV, int bias_n) {
 }
 
 // EXACT: dim = vdim = DMAX (the usual case): strides and loop bounds are compile-time constants.
-template <int DMAX, bool ROWS_ARE_HEADS, bool EXACT>
-__global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_softmax_attn_args a, int bias_n, int splits, float *__restrict__ partial) {
+// SIG: the weight of a visible key is sigmoid(score * scale + head_bias[h]) and nothing is normalised (no running maximum, no
+// denominator, no rescaling: the outputs are plain sums) — the same tiles, staging and products serve both kinds of attention.
+template <int DMAX, bool ROWS_ARE_HEADS, bool EXACT, bool SIG>
+__global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_softmax_attn_args a, int bias_n, int splits, float *__restrict__ partial,
+                                                                 const float *__restrict__ head_bias) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -146,6 +149,17 @@ __global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_sof
     for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float scale2 = a.scale * kLog2e;
+    float hb[2] = {0.f, 0.f};                                  // SIG: the bias of the head of rows rq and rq + 8, in log2 units
+    if constexpr (SIG) {
+        if (head_bias) {
+            if constexpr (ROWS_ARE_HEADS) {
+                hb[0] = rq < rows_w ? head_bias[h0 + rq] * kLog2e : 0.f;
+                hb[1] = rq + 8 < rows_w ? head_bias[h0 + rq + 8] * kLog2e : 0.f;
+            } else {
+                hb[0] = hb[1] = head_bias[h0] * kLog2e;
+            }
+        }
+    }
 
     // cache rows (of the CTA's key/value head) of a tile's keys, looked up once per key one tile ahead of the copies that use
     // them (-1: past the last key)
@@ -219,61 +233,78 @@ __global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_sof
                     }
                 }
             }
-            // scale, bias, mask; running maximum per row (rows rq and rq + 8)
-            float tmax[2] = {-INFINITY, -INFINITY};
             // every pair of the warp's rows and keys is visible: below the diagonal for the first row, inside the window of the
             // last row (or all kept)
             const bool all_visible = rows_w == 16 && j1 <= pw0 && (pw_last - j0 < window || j1 < keep);
             const int dist0 = pw0 + rq - j0 - 2 * t4;   // distance of (row rq, key j0 + 2 t4)
+            if constexpr (SIG) {
+                // weights: sigmoid(score * scale + bias) = 1 / (1 + 2^-(x log2 e)); zero where the key is not visible
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
+                for (int n = 0; n < NT; ++n)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int half = e >> 1, row = rq + half * 8;
-                    const int dist = ROWS_ARE_HEADS ? ctx - (j0 + n * 8 + 2 * t4 + (e & 1)) : dist0 + half * 8 - n * 8 - (e & 1);
-                    float s = sacc[n][e] * scale2;
-                    if (a.dist_bias) {
-                        if constexpr (ROWS_ARE_HEADS) {
-                            if (row < rows_w && dist >= 0) s += __ldg(a.dist_bias + static_cast<int64_t>(min(dist, last_row)) * H + h0 + row) * kLog2e;
-                        } else if (bias_n > last_row) {   // the whole table is in shared memory
-                            s += bias_s[min(max(dist, 0), last_row)];
-                        } else if (dist >= 0) {
-                            s += dist < bias_n ? bias_s[dist] : __ldg(a.dist_bias + static_cast<int64_t>(min(dist, last_row)) * H + h0) * kLog2e;
+                    for (int e = 0; e < 4; ++e) {
+                        const int half = e >> 1, row = rq + half * 8;
+                        const int dist = ROWS_ARE_HEADS ? ctx - (j0 + n * 8 + 2 * t4 + (e & 1)) : dist0 + half * 8 - n * 8 - (e & 1);
+                        float pv = __frcp_rn(1.f + ex2(-fmaf(sacc[n][e], scale2, hb[half])));
+                        if (!all_visible) {
+                            const int j = (ROWS_ARE_HEADS ? ctx : pw0 + row) - dist;
+                            if (!(row < rows_w && dist >= 0 && (dist < window || j < keep))) pv = 0.f;
                         }
+                        sacc[n][e] = pv;
                     }
-                    if (!all_visible) {
-                        const int j = (ROWS_ARE_HEADS ? ctx : pw0 + row) - dist;
-                        if (!(row < rows_w && dist >= 0 && (dist < window || j < keep))) s = -INFINITY;
+            } else {
+                // scale, bias, mask; running maximum per row (rows rq and rq + 8)
+                float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int half = e >> 1, row = rq + half * 8;
+                        const int dist = ROWS_ARE_HEADS ? ctx - (j0 + n * 8 + 2 * t4 + (e & 1)) : dist0 + half * 8 - n * 8 - (e & 1);
+                        float s = sacc[n][e] * scale2;
+                        if (a.dist_bias) {
+                            if constexpr (ROWS_ARE_HEADS) {
+                                if (row < rows_w && dist >= 0) s += __ldg(a.dist_bias + static_cast<int64_t>(min(dist, last_row)) * H + h0 + row) * kLog2e;
+                            } else if (bias_n > last_row) {   // the whole table is in shared memory
+                                s += bias_s[min(max(dist, 0), last_row)];
+                            } else if (dist >= 0) {
+                                s += dist < bias_n ? bias_s[dist] : __ldg(a.dist_bias + static_cast<int64_t>(min(dist, last_row)) * H + h0) * kLog2e;
+                            }
+                        }
+                        if (!all_visible) {
+                            const int j = (ROWS_ARE_HEADS ? ctx : pw0 + row) - dist;
+                            if (!(row < rows_w && dist >= 0 && (dist < window || j < keep))) s = -INFINITY;
+                        }
+                        sacc[n][e] = s;
+                        tmax[half] = fmaxf(tmax[half], s);
                     }
-                    sacc[n][e] = s;
-                    tmax[half] = fmaxf(tmax[half], s);
+                float corr[2], msub[2];
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    tmax[hf] = fmaxf(tmax[hf], __shfl_xor_sync(0xffffffffu, tmax[hf], 1));
+                    tmax[hf] = fmaxf(tmax[hf], __shfl_xor_sync(0xffffffffu, tmax[hf], 2));
+                    const float m_new = fmaxf(m_run[hf], tmax[hf]);
+                    msub[hf] = m_new == -INFINITY ? 0.f : m_new;          // a row that has seen nothing yet: exp2(-inf - 0) = 0
+                    corr[hf] = m_run[hf] == -INFINITY ? 0.f : ex2(m_run[hf] - msub[hf]);
+                    m_run[hf] = m_new;
+                    l_run[hf] *= corr[hf];
                 }
-            float corr[2], msub[2];
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                tmax[hf] = fmaxf(tmax[hf], __shfl_xor_sync(0xffffffffu, tmax[hf], 1));
-                tmax[hf] = fmaxf(tmax[hf], __shfl_xor_sync(0xffffffffu, tmax[hf], 2));
-                const float m_new = fmaxf(m_run[hf], tmax[hf]);
-                msub[hf] = m_new == -INFINITY ? 0.f : m_new;          // a row that has seen nothing yet: exp2(-inf - 0) = 0
-                corr[hf] = m_run[hf] == -INFINITY ? 0.f : ex2(m_run[hf] - msub[hf]);
-                m_run[hf] = m_new;
-                l_run[hf] *= corr[hf];
-            }
+                for (int n = 0; n < NT; ++n)
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
+                    for (int e = 0; e < 4; ++e) {
+                        const float pv = ex2(sacc[n][e] - msub[e >> 1]);
+                        sacc[n][e] = pv;
+                        l_run[e >> 1] += pv;
+                    }
+                if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // no row's maximum moved: nothing to rescale
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float pv = ex2(sacc[n][e] - msub[e >> 1]);
-                    sacc[n][e] = pv;
-                    l_run[e >> 1] += pv;
-                }
-            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // no row's maximum moved: nothing to rescale
-#pragma unroll
-                for (int n = 0; n < DMAX / 8; ++n) {
-                    o[n][0] *= corr[0];
-                    o[n][1] *= corr[0];
-                    o[n][2] *= corr[1];
-                    o[n][3] *= corr[1];
+                    for (int n = 0; n < DMAX / 8; ++n) {
+                        o[n][0] *= corr[0];
+                        o[n][1] *= corr[0];
+                        o[n][2] *= corr[1];
+                        o[n][3] *= corr[1];
+                    }
                 }
             }
 #pragma unroll
@@ -312,7 +343,7 @@ __global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_sof
         for (int hf = 0; hf < 2; ++hf) {
             const int row = rq + hf * 8;
             if (row >= rows_w) continue;
-            const float inv = 1.f / l_run[hf];
+            const float inv = SIG ? 1.f : 1.f / l_run[hf];
 #pragma unroll
             for (int n = 0; n < DMAX / 8; ++n) {
                 if (n * 8 < DV) {
@@ -337,7 +368,7 @@ __global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_sof
         for (int hf = 0; hf < 2; ++hf) {
             const int row = rq + hf * 8;
             if (t4 == 0) {
-                m_s[warp * 16 + row] = m_run[hf];
+                m_s[warp * 16 + row] = SIG ? 0.f : m_run[hf];
                 l_s[warp * 16 + row] = l_run[hf];
             }
 #pragma unroll
@@ -365,11 +396,11 @@ __global__ void __launch_bounds__(128, 3) softmax_attn_tc_kernel(const atoma_sof
                 float *pm = partial + ((static_cast<int64_t>(b) * H + h) * splits + split) * (DV + 2);
                 if (d == 0) {
                     pm[0] = M;
-                    pm[1] = Lsum;
+                    pm[1] = SIG ? (split == 0 ? 1.f : 0.f) : Lsum;   // SIG: the merge divides the plain sum of the splits by one
                 }
                 pm[2 + d] = acc;
             } else {
-                float v = acc / Lsum;
+                float v = SIG ? acc : acc / Lsum;
                 if (a.gate) v *= sigmoidf_(__bfloat162float(static_cast<const __nv_bfloat16 *>(a.gate)[static_cast<int64_t>(tok0) * a.ld_gate + h * DV + d]));
                 static_cast<__nv_bfloat16 *>(a.out)[(static_cast<int64_t>(tok0) * H + h) * DV + d] = __float2bfloat16_rn(v);
             }
@@ -405,27 +436,30 @@ __global__ void __launch_bounds__(128) softmax_split_merge_kernel(const atoma_so
     }
 }
 
-template <int DMAX, bool ROWS_ARE_HEADS, bool EXACT>
-cudaError_t launch_tc_exact(const atoma_softmax_attn_args &a, dim3 grid, size_t smem, int bias_n, int splits, float *partial, cudaStream_t stream) {
+template <int DMAX, bool ROWS_ARE_HEADS, bool EXACT, bool SIG>
+cudaError_t launch_tc_exact(const atoma_softmax_attn_args &a, dim3 grid, size_t smem, int bias_n, int splits, float *partial, const float *head_bias,
+                            cudaStream_t stream) {
     static int attr_dev = -1;
     const int dev = current_device_info().ordinal;
     if (attr_dev != dev) {
-        cudaFuncSetAttribute(softmax_attn_tc_kernel<DMAX, ROWS_ARE_HEADS, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        cudaFuncSetAttribute(softmax_attn_tc_kernel<DMAX, ROWS_ARE_HEADS, EXACT, SIG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
         attr_dev = dev;
     }
-    return launch_ex(softmax_attn_tc_kernel<DMAX, ROWS_ARE_HEADS, EXACT>, grid, dim3(128), smem, stream, a, bias_n, splits, partial);
+    return launch_ex(softmax_attn_tc_kernel<DMAX, ROWS_ARE_HEADS, EXACT, SIG>, grid, dim3(128), smem, stream, a, bias_n, splits, partial, head_bias);
 }
-template <int DMAX, bool ROWS_ARE_HEADS>
-cudaError_t launch_tc(const atoma_softmax_attn_args &a, dim3 grid, size_t smem, int bias_n, int splits, float *partial, cudaStream_t stream) {
-    return (a.dim == DMAX && a.vdim == DMAX) ? launch_tc_exact<DMAX, ROWS_ARE_HEADS, true>(a, grid, smem, bias_n, splits, partial, stream)
-                                             : launch_tc_exact<DMAX, ROWS_ARE_HEADS, false>(a, grid, smem, bias_n, splits, partial, stream);
+template <int DMAX, bool ROWS_ARE_HEADS, bool SIG>
+cudaError_t launch_tc(const atoma_softmax_attn_args &a, dim3 grid, size_t smem, int bias_n, int splits, float *partial, const float *head_bias,
+                      cudaStream_t stream) {
+    return (a.dim == DMAX && a.vdim == DMAX) ? launch_tc_exact<DMAX, ROWS_ARE_HEADS, true, SIG>(a, grid, smem, bias_n, splits, partial, head_bias, stream)
+                                             : launch_tc_exact<DMAX, ROWS_ARE_HEADS, false, SIG>(a, grid, smem, bias_n, splits, partial, head_bias, stream);
 }
 
 }  // namespace
 
 // Takes bfloat16 batches whose head sizes are multiples of 16 up to 128.  Sequences with one token in the step (decoded
 // tokens) run with the heads of a key/value group as the tile's rows, the others by query tile; a mixed batch launches both.
-bool hyb_softmax_attention_tc(const atoma_softmax_attn_args &a, cudaStream_t stream, bool *taken) {
+template <bool SIG>
+bool attention_tc(const atoma_softmax_attn_args &a, const float *head_bias, cudaStream_t stream, bool *taken) {
     *taken = false;
     const int64_t kmax = std::max(a.dim, a.vdim);
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -454,8 +488,8 @@ bool hyb_softmax_attention_tc(const atoma_softmax_attn_args &a, cudaStream_t str
             if (!partial) return false;
         }
         const dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(a.B), static_cast<unsigned>(a.G * chunks));
-        const cudaError_t e = kmax <= 64 ? launch_tc<64, true>(a, grid, smem, 0, splits, partial, stream)
-                                         : launch_tc<128, true>(a, grid, smem, 0, splits, partial, stream);
+        const cudaError_t e = kmax <= 64 ? launch_tc<64, true, SIG>(a, grid, smem, 0, splits, partial, head_bias, stream)
+                                         : launch_tc<128, true, SIG>(a, grid, smem, 0, splits, partial, head_bias, stream);
         if (!hybrid::launched(e, "softmax_attn_tc_kernel<heads>")) return false;
         if (splits > 1 &&
             !hybrid::launched(launch_ex(softmax_split_merge_kernel, dim3(static_cast<unsigned>(a.B), static_cast<unsigned>(a.H)), dim3(128), 0, stream,
@@ -468,9 +502,42 @@ bool hyb_softmax_attention_tc(const atoma_softmax_attn_args &a, cudaStream_t str
     const int bias_n = a.dist_bias ? static_cast<int>(std::min<int64_t>(a.dist_rows, kBiasSmem)) : 0;
     const TcLayout L = tc_layout(D, DV, bias_n);
     const dim3 grid(static_cast<unsigned>((a.max_query_len + kRowsCta - 1) / kRowsCta), static_cast<unsigned>(a.B), static_cast<unsigned>(a.H));
-    const cudaError_t e = kmax <= 64 ? launch_tc<64, false>(a, grid, L.total, bias_n, 1, nullptr, stream)
-                                     : launch_tc<128, false>(a, grid, L.total, bias_n, 1, nullptr, stream);
+    const cudaError_t e = kmax <= 64 ? launch_tc<64, false, SIG>(a, grid, L.total, bias_n, 1, nullptr, head_bias, stream)
+                                     : launch_tc<128, false, SIG>(a, grid, L.total, bias_n, 1, nullptr, head_bias, stream);
     return hybrid::launched(e, "softmax_attn_tc_kernel<tokens>");
+}
+
+bool hyb_softmax_attention_tc(const atoma_softmax_attn_args &a, cudaStream_t stream, bool *taken) {
+    return attention_tc<false>(a, nullptr, stream, taken);
+}
+
+// Sigmoid attention whose heads do not talk to each other (no slopes, no cap on the scores, no mixing of the heads' weights: the
+// caller knows) on the same kernels: weights sigmoid(score * scale + head_bias[h]), outputs the plain weighted sums.
+bool hyb_sigmoid_attention_tc(const atoma_sigmoid_attn_args &s, cudaStream_t stream, bool *taken) {
+    *taken = false;
+    if (s.talk || s.softcap != 0.f || !s.query_start) return true;
+    atoma_softmax_attn_args a{};
+    a.q = s.q;
+    a.k_cache = s.k_cache;
+    a.v_cache = s.v_cache;
+    a.out = s.out;
+    a.positions = s.positions;
+    a.token_seq = s.token_seq;
+    a.query_start = s.query_start;
+    a.block_tables = s.block_tables;
+    a.T = s.T;
+    a.B = s.B;
+    a.max_blocks = s.max_blocks;
+    a.H = s.H;
+    a.G = s.G;
+    a.dim = s.dim;
+    a.vdim = s.vdim;
+    a.block_size = s.block_size;
+    a.scale = s.scale;
+    a.dtype = s.dtype;
+    a.max_query_len = s.max_query_len;
+    a.max_seq_len = s.max_seq_len;
+    return attention_tc<true>(a, s.head_bias, stream, taken);
 }
 
 }  // namespace atoma

@@ -208,6 +208,9 @@ def run(args, torch, dev, json_fd):
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     page = 16
     out_sizes, headline = {}, None
+    import time
+    from bench import ClockSampler
+    sampler, t_clock0 = ClockSampler(torch.cuda.current_device()), time.time()
     for name, s in SIZES.items():
         spec = _spec(s)
         weights = _weights(torch, spec, s, dev)
@@ -257,12 +260,13 @@ def run(args, torch, dev, json_fd):
             "kernels": rows,
         }
         headline = out_sizes[name]
+    clocks = sampler.stop(t_clock0, time.time())             # all of the run: every size's model steps and kernel rows are timed regions
     line = {
         "metric": "Surinex decode tokens/s, batch 32, context 4096, 4k-wide layer sizes (5 layer runs), through the engine's executor",
         "value": headline["decode_graph_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": headline["decode_graph_ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights, random tokens)", "impl": "ours",
-        "gpu_launches": headline["decode_launches_per_step"],
+        "gpu_launches": headline["decode_launches_per_step"], "clocks": clocks,
         "e2e": {"value": headline["decode_tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": headline["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": headline["d2h_bytes_per_step"]},
         "config": {"design": "Surinex", "batch": BATCH, "ctx": CTX, "prompt": PROMPT, "peaks": src, "hbm_gbs": hbm, "bf16_tflops": tf,

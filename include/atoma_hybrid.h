@@ -100,7 +100,7 @@ typedef struct atoma_sigmoid_attn_args {
     const int32_t *token_seq;     /* [T] batch row of every token */
     const int32_t *query_start;   /* [B + 1] first token of every batch row (rows are contiguous, positions ascending) */
     const int32_t *block_tables;  /* [B, max_blocks] */
-    const float *slopes, *head_bias, *talk; /* [H], [H], [H, H] */
+    const float *slopes, *head_bias, *talk; /* [H] (NULL: no distance term), [H], [H, H] (NULL: the heads do not talk) */
     int64_t T, B, max_blocks, H, G, dim, vdim, block_size;
     float scale, softcap;
     uint32_t dtype;

@@ -353,7 +353,7 @@ def test_rotary_sigmoid_attention_on_a_mixed_batch(dtype, general, H, G, D, V, d
         slot = torch.tensor([rows[b][p] for b, (lo, hi) in zip(members, spans) for p in range(lo, hi)], dtype=torch.int64, device=DEV)
         q = ops.qkv_headnorm_rope_cache(x, 0, H * D, H * D + G * D, qn.to(DEV), kn.to(DEV), fq, fv, il, pos, slot, kc, vc, H, G, D, V, eps)
         tseq, qs = batch_layout([hi - lo for lo, hi in spans])
-        out = ops.sigmoid_attention_paged(q, kc, vc, pos, tseq, bt[members].contiguous().to(DEV), torch.zeros(H, device=DEV), pb.to(DEV), None,
+        out = ops.sigmoid_attention_paged(q, kc, vc, pos, tseq, bt[members].contiguous().to(DEV), None, pb.to(DEV), None,
                                           H, G, D, V, bs, scale, 0.0, max(hi - lo for lo, hi in spans), query_start=qs,
                                           max_seq_len=max(hi for _, hi in spans))
         return ops.rotate_heads(out, pos, fv, H, V, il, -1.0)
@@ -366,6 +366,47 @@ def test_rotary_sigmoid_attention_on_a_mixed_batch(dtype, general, H, G, D, V, d
                                     scale, H, G, D, V, eps)[starts[b]:]
         assert nerr(got[at:at + want.shape[0]], want) < tol(dtype, 2e-5, 2e-2), b
         at += want.shape[0]
+
+
+@pytest.mark.parametrize("H,G,D,V", [(4, 2, 32, 32), (6, 3, 64, 32), (2, 1, 128, 128), (20, 1, 16, 48)])
+def test_sigmoid_attention_of_independent_heads_over_long_contexts(H, G, D, V):
+    """bfloat16 heads that do not talk to each other run on key tiles: a 700-token portion that continues a 300-token context (many
+    query tiles, the diagonal inside a tile), a whole 130-token prompt, and single tokens after 1500 and 70 cached ones (keys split
+    over several CTAs and merged; more heads per key/value head than a tile has rows), on shuffled pages, against plain sums."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(H * 10 + D)
+    bs, scale = 16, D ** -0.5
+    spans = [(300, 1000), (0, 130), (1500, 1501), (70, 71)]                 # tokens of the step: positions lo .. hi - 1
+    lens = [hi for _, hi in spans]
+    bt, rows, n_rows = paged(lens, bs, len(lens), g)
+    ks = [bf(rnd(g, n, G, D)) for n in lens]
+    vs = [bf(rnd(g, n, G, V)) for n in lens]
+    qs_ = [bf(rnd(g, hi - lo, H, D, scale=2.0)) for lo, hi in spans]
+    pb = rnd(g, H, shift=-3.0)
+    kc = torch.zeros((n_rows, G, D), dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros((n_rows, G, V), dtype=torch.bfloat16, device=DEV)
+    for b in range(len(lens)):
+        idx = torch.tensor(rows[b], device=DEV)
+        kc[idx], vc[idx] = ks[b].to(torch.bfloat16).to(DEV), vs[b].to(torch.bfloat16).to(DEV)
+    q = torch.cat(qs_).reshape(-1, H * D).to(torch.bfloat16).to(DEV)
+    pos = torch.cat([torch.arange(lo, hi) for lo, hi in spans]).to(DEV)
+    tseq, qs = batch_layout([hi - lo for lo, hi in spans])
+    outs = []
+    for flags in (0, 2):
+        ops.debug_flags(flags)
+        outs.append(ops.sigmoid_attention_paged(q, kc, vc, pos, tseq, bt.to(DEV), None, pb.to(DEV), None, H, G, D, V, bs, scale, 0.0,
+                                                max(hi - lo for lo, hi in spans), query_start=qs, max_seq_len=max(lens)))
+    at = 0
+    for b, (lo, hi) in enumerate(spans):
+        k, v, qq = ks[b].double(), vs[b].double(), qs_[b].double()
+        kh, vh = k.repeat_interleave(H // G, 1), v.repeat_interleave(H // G, 1)          # [n, H, .]
+        sc = torch.einsum("ihd,jhd->hij", qq, kh) * scale + pb.double()[:, None, None]
+        vis = torch.arange(hi)[None, :] <= torch.arange(lo, hi)[:, None]
+        w = so.sigma(sc) * vis[None]
+        want = torch.einsum("hij,jhv->ihv", w, vh).reshape(hi - lo, H * V)
+        for got in outs:
+            assert nerr(got[at:at + hi - lo], want) < 1e-2, (b, nerr(got[at:at + hi - lo], want))
+        at += hi - lo
 
 
 @pytest.mark.parametrize("decode", [False, True])
@@ -393,7 +434,7 @@ def test_one_loud_key_far_back_carries_its_value_home(far, decode):
     spans = [(0, n)] if not decode else [(0, n - 1), (n - 1, n)]
     for lo, hi in spans:
         qd = ops.qkv_headnorm_rope_cache(proj[lo:hi].to(DEV), 0, D, 2 * D, None, None, None, fv, True, pos[lo:hi], slot[lo:hi], kc, vc, H, G, D, V, 1e-5)
-        out = ops.sigmoid_attention_paged(qd, kc, vc, pos[lo:hi], i32([0] * (hi - lo)), bt.to(DEV), torch.zeros(H, device=DEV), pb.to(DEV), None,
+        out = ops.sigmoid_attention_paged(qd, kc, vc, pos[lo:hi], i32([0] * (hi - lo)), bt.to(DEV), None, pb.to(DEV), None,
                                           H, G, D, V, bs, 1.0, 0.0, hi - lo, query_start=i32([0, hi - lo]), max_seq_len=hi)
         out = ops.rotate_heads(out, pos[lo:hi], fv, H, V, True, -1.0)
     want = so.rotate(v[0:1].double().reshape(1, 1, V), [-(n - 1)], f, "interleaved").reshape(V)
