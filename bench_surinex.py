@@ -191,6 +191,39 @@ def _kernel_rows(torch, s, dev, steps, warmup, hbm, tf):
     of, gate, hw = torch.randn((T, H * V), device=dev), rn(T, H * V), torch.ones(V, device=dev)
     f = lambda: ho.headnorm_gate(of, hw, gate, H, V, 1e-5, bf)
     rows["headnorm_gate"] = _row(_time(torch, f, steps, warmup, flush), nbytes=T * H * V * (4 + 2 + 2), hbm=hbm)
+    del proj, kc, vc, o, of, gate
+    torch.cuda.empty_cache()
+    # ---- attention: one 4096-token prompt, and a decode step of BATCH sequences at context CTX ----
+    page = 16
+    pb, talk = torch.zeros(H, device=dev) - 3, torch.eye(H, device=dev) + 0.05
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
+    l = s["latent"]
+    LH, R, Rk = l["heads"], l["kv_rank"] + l["rot_dim"], l["kv_rank"]
+    for name, T, B, ctx in (("prefill", PROMPT, 1, 0), ("decode", BATCH, BATCH, CTX)):
+        n = T // B
+        mb = (ctx + n + page - 1) // page
+        bt = torch.randperm(B * mb, device=dev).to(torch.int32).reshape(B, mb)
+        pos = (torch.arange(n, device=dev) + ctx).repeat(B)
+        tseq, qs = torch.arange(B, device=dev, dtype=torch.int32).repeat_interleave(n), i32([i * n for i in range(B + 1)])
+        kc, vc, q = rn(B * mb * page, G, D), rn(B * mb * page, G, V), rn(T, H * D)
+        pairs = B * (n * ctx + n * (n + 1) / 2)
+        mine = lambda: ho.sigmoid_attention_paged(q, kc, vc, pos, tseq, bt, None, pb, None, H, G, D, V, page, D ** -0.5, 0.0, n, query_start=qs,
+                                                  max_seq_len=ctx + n)
+        like = lambda: ho.sigmoid_attention_paged(q, kc, vc, pos, tseq, bt, slopes, pb, talk, H, G, D, V, page, D ** -0.5, 30.0, n, query_start=qs,
+                                                  max_seq_len=ctx + n)
+        for key, f in ((f"sigmoid_attention_{name}", mine), (f"lilovik_sigmoid_attention_{name}", like)):
+            rows[key] = _row(_time(torch, f, steps, warmup, flush), nbytes=B * (ctx + n) * G * (D + V) * 2, hbm=hbm, flops=2.0 * pairs * H * (D + V), tf=tf)
+        del kc, vc, q
+        cache, ql = rn(B * mb * page, R), torch.randn((T, LH * R), device=dev) * 0.1
+        f = lambda: ho.latent_attention_paged(ql, cache, pos, tseq, bt, None, LH, R, page, 0, R ** -0.5, n, query_start=qs, max_seq_len=ctx + n, out_cols=Rk)
+        rows[f"latent_attention_{name}"] = _row(_time(torch, f, steps, warmup, flush), nbytes=B * (ctx + n) * R * 2, hbm=hbm, flops=2.0 * pairs * LH * (R + Rk), tf=tf)
+        if name == "decode":                                 # the like kernel: the same operator on rows without a score-only tail
+            qk, ck = ql[:, :LH * Rk].contiguous(), cache[:, :Rk].contiguous()
+            f = lambda: ho.latent_attention_paged(qk, ck, pos, tseq, bt, None, LH, Rk, page, 0, R ** -0.5, n, query_start=qs, max_seq_len=ctx + n)
+            rows["patadra_latent_attention_decode"] = _row(_time(torch, f, steps, warmup, flush), nbytes=B * (ctx + n) * Rk * 2, hbm=hbm,
+                                                           flops=4.0 * pairs * LH * Rk, tf=tf)
+            del qk, ck
+        del cache, ql
     return rows
 
 
